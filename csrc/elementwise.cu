@@ -524,3 +524,50 @@ B200_API int b200_fold_grad(void* x, float* y, long long n, float scale, int cle
   B200_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Clamped gated unit:  g = min(gate, limit), u = clamp(up, -limit, limit);  y = g * sigmoid(alpha * g) * (u + shift)
+// gu: [rows, 2F] (gate | up), y: [rows, F]. limit <= 0 switches the clamps off.
+// Logit soft cap, in place on fp32:  x <- cap * tanh(x / cap)
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha,
+                                   float shift) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * F) return;
+  const long long r = idx / F;
+  const int c = (int)(idx - r * F);
+  float g = to_f32<T>(gu[r * 2 * F + c]);
+  float u = to_f32<T>(gu[r * 2 * F + F + c]);
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  const float sig = 1.f / (1.f + expf(-alpha * g));
+  y[idx] = from_f32<T>(g * sig * (u + shift));
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+}  // namespace b200
+
+B200_API int b200_clamped_glu(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, int dtype,
+                              void* stream) {
+  using namespace b200;
+  if (rows <= 0 || F <= 0) return rows == 0 ? 0 : B200_ERR_BAD_SHAPE;
+  const int tb = 256;
+  const unsigned grid = (unsigned)((rows * F + tb - 1) / tb);
+  B200_DISPATCH_T(dtype, clamped_glu_kernel<T><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift));
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_softcap(float* x, long long n, float cap, void* stream) {
+  if (n <= 0) return 0;
+  b200::softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, cap);
+  B200_LAUNCH_CHECK();
+  return 0;
+}

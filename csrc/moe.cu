@@ -1,0 +1,108 @@
+// Mixture-of-experts routing and combination around the grouped GEMMs.
+//
+//   b200_moe_route     router logits z = W_r h (+ bias) in fp32 (h may be 16-bit, W_r 16-bit or fp32), the `top` largest
+//                      experts per token and their weights. mode 0: softmax over the chosen logits only; mode 1: softmax
+//                      over all experts, chosen probabilities kept as they are; mode 2: mode 1 renormalised to sum 1.
+//                      One warp per token; ties go to the lower expert index.
+//   b200_moe_combine   out[t] = sum_k p[t, k] * y[dest[t * top + k]] in fp32 (y: the expert-sorted rows the grouped GEMM
+//                      wrote), a fixed order of additions per token.
+#include "common.cuh"
+#include "../include/b200_ops.h"
+
+namespace b200 {
+
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const float* __restrict__ bias, long long* __restrict__ top_i,
+                 float* __restrict__ top_p, float* __restrict__ logits_out, long long tokens, int W, int E, int top, int mode) {
+  extern __shared__ float zbuf[];                     // [warps, E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= tokens) return;
+  float* z = zbuf + warp * E;
+  const TH* hr = h + t * W;
+  for (int e = 0; e < E; ++e) {
+    const TW* w = wr + (long long)e * W;
+    float a = 0.f;
+    for (int i = lane; i < W; i += 32) a = fmaf(to_f32<TH>(hr[i]), to_f32<TW>(w[i]), a);
+    a = warp_sum(a);
+    if (lane == 0) {
+      const float v = a + (bias ? bias[e] : 0.f);
+      z[e] = v;
+      if (logits_out) logits_out[t * E + e] = v;
+    }
+  }
+  __syncwarp();
+  if (lane != 0) return;
+  float zmax = -INFINITY, zsum = 0.f;
+  if (mode != 0) {
+    for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
+    for (int e = 0; e < E; ++e) zsum += expf(z[e] - zmax);
+  }
+  float first = 0.f, psum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    int best = 0;
+    float bv = z[0];
+    for (int e = 1; e < E; ++e)
+      if (z[e] > bv) { best = e; bv = z[e]; }
+    z[best] = -INFINITY;                               // taken
+    top_i[t * top + k] = best;
+    if (k == 0) first = bv;
+    const float pv = mode == 0 ? expf(bv - first) : expf(bv - zmax) / zsum;
+    top_p[t * top + k] = pv;
+    psum += pv;
+  }
+  if (mode == 0 || mode == 2)
+    for (int k = 0; k < top; ++k) top_p[t * top + k] /= psum;
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const long long* __restrict__ dest, const float* __restrict__ p,
+                                   float* __restrict__ out, long long tokens, int W, int top) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * W) return;
+  const long long t = idx / W;
+  const int c = (int)(idx - t * W);
+  float a = 0.f;
+  for (int k = 0; k < top; ++k) a = fmaf(p[t * top + k], to_f32<T>(y[dest[t * top + k] * W + c]), a);
+  out[idx] = a;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+B200_API int b200_moe_route(const void* h, const void* wr, const float* bias, long long* top_i, float* top_p, float* logits_out,
+                            long long tokens, int W, int E, int top, int mode, int h_dtype, int w_dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens <= 0) return 0;
+  if (W <= 0 || E <= 0 || top <= 0 || top > E || E > 2048) return B200_ERR_BAD_SHAPE;
+  const int warps = 4;
+  const unsigned grid = (unsigned)((tokens + warps - 1) / warps);
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  typedef __nv_bfloat16 bf;
+#define RT(TH, TW)                                                                                                          \
+  moe_route_kernel<TH, TW><<<grid, warps * 32, smem, st>>>((const TH*)h, (const TW*)wr, bias, top_i, top_p, logits_out, tokens, W, \
+                                                          E, top, mode)
+  if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_BF16) RT(bf, bf);
+  else if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_FP32) RT(bf, float);
+  else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_FP32) RT(float, float);
+  else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_BF16) RT(float, bf);
+  else return B200_ERR_UNSUPPORTED;
+#undef RT
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_moe_combine(const void* y, const long long* dest, const float* p, float* out, long long tokens, int W, int top,
+                              int dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens <= 0) return 0;
+  const unsigned grid = (unsigned)((tokens * W + 255) / 256);
+  if (dtype == B200_DT_BF16) moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, dest, p, out, tokens, W, top);
+  else if (dtype == B200_DT_FP16) moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)y, dest, p, out, tokens, W, top);
+  else if (dtype == B200_DT_FP32) moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)y, dest, p, out, tokens, W, top);
+  else return B200_ERR_UNSUPPORTED;
+  B200_LAUNCH_CHECK();
+  return 0;
+}

@@ -416,3 +416,91 @@ B200_API int b200_norm_bwd_noalloc(int layer_norm, const void* dy, const void* h
   B200_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Sandwich norms around a 32-bit residual stream (pre- and post-sublayer RMSNorm, gain stored as an offset from `off`):
+//     x   = res + rms(y) * (off + w_post)        (w_post == nullptr: x = res + y;  res_in == nullptr: res = 0)
+//     h   = rms(x) * (off + w_next)              (w_next == nullptr: h is not written)
+// x is written to the fp32 stream `res_out`; y and h have their own types (fp32 or 16-bit). One CTA per row, the row is
+// kept in shared memory between the passes, all statistics and the stream itself are fp32.
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+template <typename TY, typename TH, typename WT>
+__global__ void __launch_bounds__(kNormThreads)
+sandwich_norm_kernel(const TY* __restrict__ y, const WT* __restrict__ w_post, const float* __restrict__ res_in,
+                     float* __restrict__ res_out, const WT* __restrict__ w_next, TH* __restrict__ h, int cols, float eps,
+                     float off) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  float ss = 0.f;
+  if (y) {
+    const TY* yr = y + row * cols;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float v = to_f32<TY>(yr[i]);
+      rowbuf[i] = v;
+      ss += v * v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) rowbuf[i] = 0.f;
+  }
+  float r1 = 1.f;
+  if (w_post) {
+    ss = block_sum(ss, red);
+    r1 = 1.f / sqrtf(ss / (float)cols + eps);
+  }
+  __syncthreads();
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = rowbuf[i];
+    if (w_post) v = v * r1 * (off + to_f32<WT>(w_post[i]));
+    if (res_in) v += res_in[row * cols + i];
+    rowbuf[i] = v;
+    if (res_out) res_out[row * cols + i] = v;
+    s2 += v * v;
+  }
+  if (!w_next) return;
+  s2 = block_sum(s2, red);
+  const float r2 = 1.f / sqrtf(s2 / (float)cols + eps);
+  for (int i = threadIdx.x; i < cols; i += blockDim.x)
+    h[row * cols + i] = from_f32<TH>(rowbuf[i] * r2 * (off + to_f32<WT>(w_next[i])));
+}
+
+template <typename TY, typename TH, typename WT>
+static int sandwich_launch(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
+                           long long rows, int cols, float eps, float off, cudaStream_t st) {
+  const size_t smem = (size_t)cols * sizeof(float);
+  auto kern = sandwich_norm_kernel<TY, TH, WT>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  kern<<<(unsigned)rows, kNormThreads, smem, st>>>((const TY*)y, (const WT*)w_post, res_in, res_out, (const WT*)w_next, (TH*)h,
+                                                   cols, eps, off);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+}  // namespace b200
+
+B200_API int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next,
+                                void* h, long long rows, int cols, float eps, float off, int y_dtype, int h_dtype, int w_dtype,
+                                void* stream) {
+  using namespace b200;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows <= 0) return 0;
+  if (cols <= 0) return B200_ERR_BAD_SHAPE;
+  typedef __nv_bfloat16 bf;
+#define SW(TY, TH, WT) return sandwich_launch<TY, TH, WT>(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, st)
+  if (w_dtype == B200_DT_BF16) {
+    if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_BF16) SW(float, bf, bf);
+    if (y_dtype == B200_DT_BF16 && h_dtype == B200_DT_BF16) SW(bf, bf, bf);
+    if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_FP32) SW(float, float, bf);
+    if (y_dtype == B200_DT_BF16 && h_dtype == B200_DT_FP32) SW(bf, float, bf);
+  } else if (w_dtype == B200_DT_FP32) {
+    if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_FP32) SW(float, float, float);
+    if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_BF16) SW(float, bf, float);
+    if (y_dtype == B200_DT_BF16 && h_dtype == B200_DT_BF16) SW(bf, bf, float);
+  }
+#undef SW
+  return B200_ERR_UNSUPPORTED;
+}

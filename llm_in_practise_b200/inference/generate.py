@@ -102,8 +102,11 @@ class PagedKVCache(KVCache):
     def __init__(self, n_layers, num_blocks, Hkv, block_size, D, dtype, device, max_seqs, max_len):
         if block_size & (block_size - 1):
             raise ValueError("block_size must be a power of two")
-        self.k = [torch.zeros(num_blocks, Hkv, block_size, D, dtype=dtype, device=device) for _ in range(n_layers)]
-        self.v = [torch.zeros(num_blocks, Hkv, block_size, D, dtype=dtype, device=device) for _ in range(n_layers)]
+        # Hkv / D may be lists: models whose layers differ in their KV heads or head size get one pool per layer
+        hk = list(Hkv) if isinstance(Hkv, (list, tuple)) else [Hkv] * n_layers
+        hd = list(D) if isinstance(D, (list, tuple)) else [D] * n_layers
+        self.k = [torch.zeros(num_blocks, hk[i], block_size, hd[i], dtype=dtype, device=device) for i in range(n_layers)]
+        self.v = [torch.zeros(num_blocks, hk[i], block_size, hd[i], dtype=dtype, device=device) for i in range(n_layers)]
         self.block_size, self.num_blocks = block_size, num_blocks
         self.max_len = max_len
         self.max_blocks = -(-max_len // block_size)

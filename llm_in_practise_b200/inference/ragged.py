@@ -1,0 +1,146 @@
+"""Runner for models whose compute path is the ragged serving step (``model.forward_ragged``): one call takes any mix of
+prompt pieces and single decoded tokens of different sequences, with all K/V in a paged cache.
+
+``RaggedGenerator`` is what ``Generator`` is for the Qwen family — the object ``serve.engine.LLMEngine`` schedules onto and
+``model.generate`` runs — but it has ONE forward entry, ``step``: whole prompts, pieces of prompts, decode batches and
+mixtures of them are the same call with different token lists, so a position's logits cannot depend on how its prompt was
+cut or on what shared the batch. The cache helpers of ``Generator`` (block rows, host off-load of cached prefixes) are
+inherited: they only touch the cache object.
+
+The reference reaches the same behaviour through vLLM's scheduler (chunked prefill mixed into decode batches,
+Deployment/Ray/serve_run_examples/deepseek.py:29-34).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .generate import GenerationConfig, Generator, PagedKVCache, sample_next
+
+TILE_Q = 64          # query rows per tile of the tensor-core attention kernel
+
+
+@dataclass
+class Pieces:
+    """Runs of consecutive tokens of one sequence inside a step, cut into tiles of at most ``TILE_Q`` query rows:
+    ``tiles`` int32 [n_tiles, 4] = (first row in the batch, rows, position of the first row, cache row)."""
+    tiles: torch.Tensor
+    slot_of_tile: torch.Tensor
+    n_tiles: int
+    longest: int                    # tokens of the longest run
+
+    def use_mma(self, q: torch.Tensor, head_dim: int, window: int) -> bool:
+        import os
+        return (self.longest >= 8 and q.dtype in (torch.bfloat16, torch.float16) and head_dim % 16 == 0 and head_dim <= 128
+                and window == 0 and os.environ.get("B200_PAGED_MMA", "1") != "0")
+
+
+Entry = Tuple[int, int, Sequence[int], Sequence[int]]       # (cache row, first position, tokens, wanted indices into tokens)
+
+
+class RaggedGenerator(Generator):
+    ragged = True
+
+    def __init__(self, model, tokenizer=None, max_len: int = 4096):
+        super().__init__(model, tokenizer, max_len)
+
+    # ------------------------------------------------------------------ cache
+    def make_cache(self, num_blocks: int, block_size: int, max_seqs: int, max_len: int) -> PagedKVCache:
+        """A paged cache with one pool per layer, each sized from that layer's own (kv heads, head size). Physical block 0
+        is left to unset table entries; callers hand out blocks 1 .. num_blocks."""
+        m = self.model
+        lay = m.kv_layout()
+        return PagedKVCache(len(lay), num_blocks + 1, [g for g, _ in lay], block_size, [d for _, d in lay], m.embed_tokens.dtype,
+                            m.embed_tokens.device, max_seqs, max_len)
+
+    def kv_token_bytes(self) -> int:
+        es = self.model.embed_tokens.element_size()
+        return sum(2 * g * d * es for g, d in self.model.kv_layout())
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, entries: Sequence[Entry], cache: PagedKVCache, layer_outputs: Optional[list] = None) -> Optional[torch.Tensor]:
+        """Run the tokens of ``entries`` as one batch; their cache rows must already list blocks for the positions they
+        write. Returns the fp32 logits of the wanted tokens in entry order [n_wanted, vocab], or None if nothing is wanted
+        (the K/V of the tokens are stored all the same)."""
+        dev = self.model.embed_tokens.device
+        ids: List[int] = []
+        pos: List[int] = []
+        slot: List[int] = []
+        want: List[int] = []
+        tiles: List[List[int]] = []
+        longest = max_pos = 0
+        for row, pos0, toks, wanted in entries:
+            n = len(toks)
+            if n == 0:
+                continue
+            if pos0 + n > cache.max_len:
+                raise ValueError(f"sequence of {pos0 + n} tokens does not fit the cache rows of {cache.max_len}")
+            base = len(ids)
+            ids.extend(int(t) for t in toks)
+            pos.extend(range(pos0, pos0 + n))
+            slot.extend([row] * n)
+            want.extend(base + int(w) for w in wanted)
+            for q0 in range(0, n, TILE_Q):
+                tiles.append([base + q0, min(TILE_Q, n - q0), pos0 + q0, row])
+            longest = max(longest, n)
+            max_pos = max(max_pos, pos0 + n - 1)
+        if not ids:
+            return None
+        meta = torch.tensor(pos + slot, dtype=torch.int32).view(2, -1)
+        if dev.type == "cuda":
+            meta = meta.pin_memory().to(dev, non_blocking=True)
+            ids_t = torch.tensor(ids, dtype=torch.long).pin_memory().to(dev, non_blocking=True)
+            tl = torch.tensor(tiles, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        else:
+            ids_t = torch.tensor(ids, dtype=torch.long)
+            tl = torch.tensor(tiles, dtype=torch.int32)
+        pieces = Pieces(tl, tl[:, 3].contiguous(), len(tiles), longest)
+        want_t = torch.tensor(want, dtype=torch.long, device=dev) if want else torch.zeros(1, dtype=torch.long, device=dev)
+        logits = self.model.forward_ragged(ids_t, meta[0], meta[1], cache, want_t, max_pos=max_pos, pieces=pieces,
+                                           layer_outputs=layer_outputs)
+        return logits if want else None
+
+    # ------------------------------------------------------------------ single-process generation
+    def _generate(self, input_ids: torch.Tensor, config: Optional[GenerationConfig], streamer, seed: Optional[int],
+                  return_logprobs: bool, **kw):
+        """Same contract as ``Generator.generate``: [B, S] prompts -> [B, S + new] ids. The prompts are one ragged step, every
+        following step decodes one token per unfinished sequence."""
+        cfg = config or GenerationConfig(**{k: v for k, v in kw.items() if k in GenerationConfig.__dataclass_fields__})
+        eos = cfg.eos_token_id
+        eos = [] if cfg.ignore_eos else ([eos] if isinstance(eos, int) else list(eos or []))
+        B, S = input_ids.shape
+        dev = input_ids.device
+        total = min(self.max_len, S + cfg.max_new_tokens)
+        bs = 64
+        per = -(-total // bs)
+        key = ("gen", B, per)
+        cache = self._caches.get(key)
+        if cache is None:
+            self._caches.clear()
+            cache = self._caches[key] = self.make_cache(B * per, bs, B, per * bs)
+            for b in range(B):
+                self.set_block_row(cache, b, list(range(1 + b * per, 1 + (b + 1) * per)))
+        gen = torch.Generator(device=dev).manual_seed(seed) if seed is not None else None
+        rows = input_ids.tolist()
+        logits = self.step([(b, 0, rows[b], [S - 1]) for b in range(B)], cache)
+        out = input_ids
+        done = torch.zeros(B, dtype=torch.bool, device=dev)
+        logprobs: List[torch.Tensor] = []
+        for n in range(S, total):
+            nxt = sample_next(logits, cfg, out, gen)
+            if return_logprobs:
+                logprobs.append(logits.float().log_softmax(-1).gather(1, nxt[:, None]).squeeze(1))
+            nxt = torch.where(done, torch.full_like(nxt, cfg.pad_token_id), nxt)
+            out = torch.cat([out, nxt[:, None]], 1)
+            if streamer is not None:
+                streamer.put(nxt)
+            for e in eos:
+                done |= nxt == e
+            if bool(done.all()) or n + 1 >= total:
+                break
+            last = nxt.tolist()
+            logits = self.step([(b, n, [last[b]], [0]) for b in range(B)], cache)
+        return (out, torch.stack(logprobs, 1)) if return_logprobs else out

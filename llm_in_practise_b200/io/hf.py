@@ -148,6 +148,10 @@ def from_pretrained(path: str, dtype: torch.dtype = torch.bfloat16, torch_dtype:
         if quantization_config is not None and quantization_config.load_in_4bit:
             model.quantize_nf4(quantization_config.bnb_4bit_use_double_quant)
         return model
+    from ..models import registered_loader
+    loader = registered_loader(path) if os.path.isdir(path) else None
+    if loader is not None:                               # a design with its own config schema and tensor names
+        return loader(path, dtype, device)
     if not os.path.isfile(os.path.join(path, "config.json")):
         raise FileNotFoundError(f"{path!r} is neither a local checkpoint directory (no config.json there) nor one of the presets "
                                 f"{sorted(QWEN3_PRESETS)}; hub ids cannot be downloaded here — pass the directory the weights are in")

@@ -32,12 +32,12 @@ def _yarn_correction_dim(num_rotations: float, dim: int, base: float, max_pos: i
 
 
 def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, max_position_embeddings: Optional[int] = None,
-                  device=None):
+                  device=None, dtype=torch.float32):
     """(inverse frequencies [head_dim / 2] fp32, attention factor) for plain RoPE or the ``rope_scaling`` of an HF config
     (``rope_type`` / ``type``: ``linear``, ``yarn``, ``llama3``) — e.g. DeepSeek-R1-0528-Qwen3-8B ships YaRN with factor 4,
     which the reference's fine-tune script switches off with ``rope_scaling=None``
     (Fine-Tuning/deepseek-r1-0528-qwen3-8b-qlora.dist.py:98-112) and its vLLM servers leave on."""
-    idx = torch.arange(0, head_dim, 2, dtype=torch.float32, device=device)
+    idx = torch.arange(0, head_dim, 2, dtype=dtype, device=device)
     inv = 1.0 / (theta ** (idx / head_dim))
     kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
     if not scaling or kind in ("default", None):
@@ -337,3 +337,45 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, pos_table: Optional[torch.
     if pos_table is not None:
         out = out + pos_table[:period]
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# clamped gated unit, logit soft cap
+# ------------------------------------------------------------------------------------------------
+def clamped_glu(gate_up: torch.Tensor, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0) -> torch.Tensor:
+    """``g * sigmoid(alpha * g) * (u + shift)`` over ``gate_up = [rows, 2F]`` (gate first) with ``g = min(gate, limit)`` and
+    ``u = clamp(up, -limit, limit)``; ``limit <= 0`` leaves both unclamped, so ``(0, 1, 0)`` is SwiGLU for any F (the
+    vectorised ``swiglu`` wants F % 8 == 0). Inference only."""
+    rows, F2 = gate_up.shape
+    Fh = F2 // 2
+    if nv.use_native(gate_up):
+        gu = gate_up.contiguous()
+        y = torch.empty(rows, Fh, dtype=gu.dtype, device=gu.device)
+        fn = nv.proto("b200_clamped_glu", [vp, vp, i64, i32, f32, f32, f32, i32, vp])
+        nv.check(fn(nv.ptr(gu), nv.ptr(y), rows, Fh, limit, alpha, shift, nv.dtype_code(gu.dtype), nv.stream()), "clamped_glu")
+        nv.count_launch()
+        return y
+    g, u = gate_up[:, :Fh].float(), gate_up[:, Fh:].float()
+    if limit > 0:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + shift)).to(gate_up.dtype)
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place ``cap * tanh(logits / cap)`` on fp32 logits (no-op for ``cap`` None / 0)."""
+    if not cap:
+        return logits
+    if nv.use_native(logits) and logits.dtype == torch.float32 and logits.is_contiguous():
+        fn = nv.proto("b200_softcap", [vp, i64, f32, vp])
+        nv.check(fn(nv.ptr(logits), logits.numel(), float(cap), nv.stream()), "softcap")
+        nv.count_launch()
+        return logits
+    return logits.copy_(cap * torch.tanh(logits.float() / cap))
+
+
+def rope_tables_partial(max_pos: int, rot_dims: int, theta: float, device=None, scaling: Optional[dict] = None):
+    """cos/sin tables [max_pos, rot_dims / 2] for a rotation of the first ``rot_dims`` dimensions of a head. Frequencies and
+    angles are formed in float64 and rounded once to fp32, so that positions in the thousands keep full fp32 accuracy."""
+    inv, att = rope_inv_freq(rot_dims, theta, scaling, None, None, dtype=torch.float64)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv)
+    return (ang.cos() * att).float().to(device).contiguous(), (ang.sin() * att).float().to(device).contiguous()

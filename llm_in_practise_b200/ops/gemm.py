@@ -332,3 +332,33 @@ def gemm_w4(a: torch.Tensor, q, *, b_mn: bool = False, out: Optional[torch.Tenso
     nv.count_launch()
     del keep
     return out
+
+
+def linear_exact(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ w^T`` for inference at the precision of the operands: 16-bit operands go to the tcgen05 GEMM (fp32
+    accumulation, ``out_dtype`` output), fp32 operands to the FFMA kernel ``b200_gemm_f32_exact`` — the tensor-core route
+    would round them to TF32, which a run that asks for fp32 must not do. Operand rows whose byte stride is not a multiple
+    of 16 (K % 8 for 16-bit) cannot be described to TMA; they are multiplied in fp32 by the same FFMA kernel."""
+    out_dtype = out_dtype or x.dtype
+    if not nv.use_native(x):
+        return (x.float() @ w.float().t()).to(out_dtype)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.float32 and K % 8 == 0:
+        if M <= 16 and out_dtype in (x.dtype, torch.float32):
+            y = gemv16(x, w, out_dtype=out_dtype)
+            if y is not None:
+                return y
+        return gemm(x, w, out_dtype=out_dtype)
+    xf = x if x.dtype == torch.float32 else x.float()
+    wf = w if w.dtype == torch.float32 else w.float()
+    if xf.stride(-1) != 1:
+        xf = xf.contiguous()
+    if wf.stride(-1) != 1:
+        wf = wf.contiguous()
+    y = torch.empty(M, N, dtype=torch.float32, device=x.device)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    fn = nv.proto("b200_gemm_f32_exact", [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp])
+    nv.check(fn(nv.ptr(xf), nv.ptr(wf), nv.ptr(y), M, N, K, xf.stride(0), wf.stride(0), y.stride(0), nv.stream()), "gemm_f32_exact")
+    nv.count_launch()
+    return y if out_dtype == torch.float32 else y.to(out_dtype)

@@ -163,3 +163,65 @@ def moe_ffn(xf: torch.Tensor, top_i: torch.Tensor, top_p: torch.Tensor, w1, b1, 
         y = post(y)
     ys = y.index_select(0, d.dest) * top_p.reshape(-1, 1).to(y.dtype)
     return torch.zeros_like(xf).index_add(0, d.tok, ys), d
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# inference-side routing and gated experts
+# ------------------------------------------------------------------------------------------------------------------
+ROUTE_SOFTMAX_SELECTED, ROUTE_SOFTMAX_ALL, ROUTE_SOFTMAX_ALL_RENORM = 0, 1, 2
+
+
+def route_topk(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+               mode: int = ROUTE_SOFTMAX_SELECTED):
+    """Router of a token-choice MoE in fp32 (``b200_moe_route``): logits ``h W_r^T + bias``, the ``top`` largest experts per
+    token (long [T, top]) and their weights (fp32 [T, top]): softmax over the chosen logits only (mode 0), the chosen
+    entries of the softmax over all experts (1), or those renormalised (2)."""
+    T, W = h.shape
+    E = w_router.shape[0]
+    if nv.use_native(h):
+        h = h.contiguous()
+        top_i = torch.empty(T, top, dtype=torch.long, device=h.device)
+        top_p = torch.empty(T, top, dtype=torch.float32, device=h.device)
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        fn = nv.proto("b200_moe_route", [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp])
+        nv.check(fn(nv.ptr(h), nv.ptr(w_router), nv.ptr(bias), nv.ptr(top_i), nv.ptr(top_p), None, T, W, E, top, mode,
+                    nv.dtype_code(h.dtype), nv.dtype_code(w_router.dtype), nv.stream()), "moe_route")
+        nv.count_launch()
+        return top_i, top_p
+    z = h.float() @ w_router.float().t()
+    if bias is not None:
+        z = z + bias.float()
+    if mode == ROUTE_SOFTMAX_SELECTED:
+        tv, ti = z.topk(top, -1)
+        return ti, tv.softmax(-1)
+    p = z.softmax(-1)
+    tv, ti = p.topk(top, -1)
+    return ti, (tv / tv.sum(-1, keepdim=True) if mode == ROUTE_SOFTMAX_ALL_RENORM else tv)
+
+
+def moe_combine(y: torch.Tensor, dest: torch.Tensor, top_p: torch.Tensor) -> torch.Tensor:
+    """fp32 [T, D]: ``sum_k top_p[t, k] * y[dest[t * top + k]]`` over the expert-sorted rows ``y`` of a grouped GEMM."""
+    T, top = top_p.shape
+    W = y.shape[1]
+    if nv.use_native(y):
+        out = torch.empty(T, W, dtype=torch.float32, device=y.device)
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        fn = nv.proto("b200_moe_combine", [vp, vp, vp, vp, i64, i32, i32, i32, vp])
+        nv.check(fn(nv.ptr(y), nv.ptr(dest), nv.ptr(top_p), nv.ptr(out), T, W, top, nv.dtype_code(y.dtype), nv.stream()), "moe_combine")
+        nv.count_launch()
+        return out
+    return (y.index_select(0, dest).float().view(T, top, W) * top_p.unsqueeze(-1)).sum(1)
+
+
+def gated_moe_ffn(h: torch.Tensor, top_i: torch.Tensor, top_p: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                  act, tile: int = TILE) -> torch.Tensor:
+    """Token-choice MoE of gated experts for inference: ``sum_k p_k * W_down[e_k] act(W_gate_up[e_k] h)`` -> fp32 [T, D].
+    ``w_gate_up`` [E, 2F, D] (gate rows first), ``w_down`` [E, D, F], ``act`` maps [rows, 2F] -> [rows, F]. Tokens are
+    counting-sorted by expert on the device (``dispatch``), both projections are one grouped GEMM each, and the weighted
+    sum over a token's experts is taken in fp32 in a fixed order (``moe_combine``)."""
+    E = w_gate_up.shape[0]
+    d = dispatch(top_i, E, tile)
+    xs = torch.zeros(d.rows, h.shape[1], dtype=h.dtype, device=h.device).index_copy(0, d.dest, h.index_select(0, d.tok))
+    mid = act(grouped_linear(xs, w_gate_up, None, d, tile))
+    y = grouped_linear(mid, w_down, None, d, tile)
+    return moe_combine(y.contiguous(), d.dest, top_p)
