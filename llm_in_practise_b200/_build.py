@@ -55,10 +55,36 @@ def _run(cmd):
     return r.stdout + r.stderr
 
 
-def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+def _manifest() -> Path:
+    return LIBDIR / "libb200ops.sources"
+
+
+def built_sources() -> set:
+    """Stems of the .cu files the present libb200ops.so was linked from (empty: no library)."""
+    m = _manifest()
+    if not (LIBDIR / "libb200ops.so").exists():
+        return set()
+    if not m.exists():
+        return {s.stem for s in CSRC.glob("*.cu")}      # a library without a manifest is a full build
+    return set(m.read_text().split())
+
+
+def build_cuda(force: bool = False, verbose: bool = False, sources=None) -> Path:
+    """Compile ``csrc/*.cu`` (or only the files whose stems are in ``sources``) and link ``libb200ops.so``. A library linked
+    from a subset carries the same name — entry points are resolved lazily, one by one, so a model that needs seven of
+    the twenty files can run after compiling seven — and a manifest beside it records what is inside; the next full build
+    (or a request for a file that is missing) relinks it."""
     LIBDIR.mkdir(parents=True, exist_ok=True)
     OBJDIR.mkdir(parents=True, exist_ok=True)
-    srcs = sorted(CSRC.glob("*.cu"))
+    every = sorted(CSRC.glob("*.cu"))
+    if sources is not None:
+        want = set(sources) | (built_sources() if not force else set())
+        srcs = [s for s in every if s.stem in want]
+        missing = set(sources) - {s.stem for s in srcs}
+        if missing:
+            raise RuntimeError(f"no such kernel source: {sorted(missing)}")
+    else:
+        srcs = every
     hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((ROOT / "include").glob("*.h"))
     out = LIBDIR / "libb200ops.so"
     nvcc = _nvcc()
@@ -73,9 +99,19 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
                 if verbose and log.strip():
                     print(log)
     objs = [OBJDIR / (s.stem + ".o") for s in srcs]
-    if force or jobs or _stale(out, objs):
-        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
+    stems = {s.stem for s in srcs}
+    if force or jobs or _stale(out, objs) or built_sources() != stems:
+        tmp = out.with_suffix(".so.tmp%d" % os.getpid())
+        _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
+        os.replace(tmp, out)
+        _manifest().write_text("\n".join(sorted(stems)) + "\n")
     return out
+
+
+def ensure_built(sources) -> Path:
+    """Make sure libb200ops.so exists, is up to date and contains ``sources`` (stems of csrc/*.cu); compiles only what is
+    missing. The call a command-line entry point makes before it touches the GPU in a fresh checkout."""
+    return build_cuda(sources=list(sources))
 
 
 def build_host(force: bool = False) -> Path:

@@ -120,11 +120,23 @@ class LLMEngine:
 
     def __init__(self, model, tokenizer=None, args: Optional[EngineArgs] = None, model_name: str = "b200-model"):
         self.args = args or EngineArgs()
-        self.gen = self.generator_cls(model, tokenizer, self.args.max_model_len)
+        gen_cls = self.generator_cls
+        if gen_cls is Generator and getattr(getattr(model, "base_model", model), "ragged", False):
+            from ..inference.ragged import RaggedGenerator
+            gen_cls = RaggedGenerator                    # models served by one ragged step (prompt pieces + decode tokens mixed)
+        self.gen = gen_cls(model, tokenizer, self.args.max_model_len)
         self.model, self.tokenizer, self.model_name = self.gen.model, tokenizer, model_name
+        self.ragged = bool(getattr(self.gen, "ragged", False))
         c = self.model.config
         self.device = self.model.embed_tokens.device
-        if self.args.gpu_memory_utilization > 0 and self.device.type == "cuda":
+        if self.ragged and self.args.block_size <= 0:
+            self.args.block_size = 64                    # the ragged step reads K/V through a block table only
+        if self.ragged:
+            if self.args.gpu_memory_utilization > 0 and self.device.type == "cuda":
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = free - (1.0 - self.args.gpu_memory_utilization) * total
+                self.args.max_num_seqs = int(max(1, min(4096, budget // (self.gen.kv_token_bytes() * self.args.max_model_len) - 1)))
+        elif self.args.gpu_memory_utilization > 0 and self.device.type == "cuda":
             # vLLM's knob: the KV pool takes what is left of `utilization x total HBM` after the weights
             free, total = torch.cuda.mem_get_info(self.device)
             budget = free - (1.0 - self.args.gpu_memory_utilization) * total
@@ -138,8 +150,11 @@ class LLMEngine:
             nb = self.args.num_kv_blocks or (self.args.max_num_seqs * per_seq)
             # physical block 0 is never handed out: table entries that were never set (the scratch row, positions a padded
             # prefill piece writes past a sequence's end) point at it
-            self.cache = PagedKVCache(c.num_hidden_layers, nb + 1, c.num_key_value_heads, BS, c.head_dim,
-                                      self.model.embed_tokens.dtype, self.device, self.args.max_num_seqs + 1, self.args.max_model_len)
+            if self.ragged:
+                self.cache = self.gen.make_cache(nb, BS, self.args.max_num_seqs + 1, self.args.max_model_len)
+            else:
+                self.cache = PagedKVCache(c.num_hidden_layers, nb + 1, c.num_key_value_heads, BS, c.head_dim,
+                                          self.model.embed_tokens.dtype, self.device, self.args.max_num_seqs + 1, self.args.max_model_len)
             self._free_blocks: List[int] = list(range(nb, 0, -1))
             self._block_ref: List[int] = [0] * (nb + 1)
             self._slot_blocks: Dict[int, List[int]] = {}
@@ -165,7 +180,8 @@ class LLMEngine:
         self._host_bytes, self._host_budget = 0, int(self.args.kv_offload_gb * 2 ** 30)
         self._host_keys = itertools.count()
         self._host_pin = -1
-        self._kv_token_bytes = 2 * c.num_hidden_layers * c.num_key_value_heads * c.head_dim * self.model.embed_tokens.element_size()
+        self._kv_token_bytes = (self.gen.kv_token_bytes() if self.ragged else
+                                2 * c.num_hidden_layers * c.num_key_value_heads * c.head_dim * self.model.embed_tokens.element_size())
         self._ids = itertools.count()
         self._cv = threading.Condition()
         self._stop = False
@@ -180,7 +196,7 @@ class LLMEngine:
     def warmup(self) -> None:
         """Capture the CUDA graphs of every prefill bucket and decode bucket up front (dummy tokens in the scratch cache
         row), so no request pays a capture (~0.1 s each) in its time to first token."""
-        if self.device.type != "cuda":
+        if self.device.type != "cuda" or self.ragged:       # the ragged step runs eagerly: nothing to capture
             return
         scratch = self.args.max_num_seqs
         for tb in self.gen._PREFILL_BUCKETS:
@@ -277,8 +293,10 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ paged KV cache: block allocator
     def _nblocks(self, n_tokens: int) -> int:
-        """Blocks that hold ``n_tokens`` plus the <= 7 dummy positions a padded prefill piece may write past them."""
-        return -(-(min(n_tokens + 8, self.args.max_model_len)) // self.args.block_size)
+        """Blocks that hold ``n_tokens`` plus the <= 7 dummy positions a padded prefill piece may write past them (the
+        ragged step pads nothing)."""
+        pad = 0 if self.ragged else 8
+        return -(-(min(n_tokens + pad, self.args.max_model_len)) // self.args.block_size)
 
     def _blocks_free(self) -> int:
         return len(self._free_blocks) - self._reserved
@@ -563,6 +581,37 @@ class LLMEngine:
         if self.args.enable_prefix_caching:
             self._index_row(r.slot, r.prompt_ids)          # later prompts may copy this (still running) row's prefix
 
+    def _admit_on_prefix(self, r: Request, src: int, P: int) -> bool:
+        """Give ``r`` a row that already holds the first ``P`` tokens of its prompt (``src``: the row the prefix was found in,
+        -1 / 0 for none) and, with a paged cache, reserve its blocks. False: the block pool cannot promise them yet."""
+        if P > 0 and src in self._cached:
+            # the prefix lives in the row of a finished sequence: continue in that very row, nothing is copied
+            del self._cached[src]
+            self._unindex_row(src)
+            r.slot = src
+            if self.paged:
+                # positions >= P of the row are rewritten: blocks past the prefix go back to the pool (some may be listed
+                # by other sequences that share a longer prefix of the old row - those keep them)
+                self._truncate_blocks(src, P // self.args.block_size)
+                if not self._admit_blocks(r):
+                    self._drop_blocks(src)
+                    self.free.append(src)
+                    r.slot = -1
+                    return False
+        else:
+            r.slot = self._take_slot(keep=src)
+            if self.paged:
+                if not self._admit_blocks(r, src if P > 0 else -1, P):
+                    self.free.append(r.slot)
+                    r.slot = -1
+                    return False
+                if P > 0:
+                    self._share_prefix(src, r.slot, P)               # both table rows list the prefix's physical blocks
+            elif P > 0:
+                self.gen.copy_prefix(self.cache, src, r.slot, P)     # the prefix belongs to a running sequence: copy its K/V
+        r.prefilled = r.cached_tokens = P
+        return True
+
     def _prefill_piece(self, r: Request, budget: int) -> int:
         """Prefill the next piece (at most ``budget`` tokens when chunking is on) of a partly cached prompt; on the last
         piece sample the first token and move the request to the decode batch. Returns the tokens processed."""
@@ -589,6 +638,8 @@ class LLMEngine:
     @torch.no_grad()
     def step(self) -> None:
         """One scheduler iteration: admit + prefill, then one batched decode step."""
+        if self.ragged:
+            return self._step_ragged()
         batch: List[Request] = []
         budget = self.args.max_prefill_tokens
         # (1) sequences whose prompt is only partly in the cache (chunked prefill / prefix hits): one more piece each
@@ -651,36 +702,10 @@ class LLMEngine:
                 budget -= L
                 batch.append(r)
                 continue
-            if P > 0 and src in self._cached:
-                # the prefix lives in the row of a finished sequence: continue in that very row, nothing is copied
-                del self._cached[src]
-                self._unindex_row(src)
-                r.slot = src
-                if self.paged:
-                    # positions >= P of the row are rewritten: blocks past the prefix go back to the pool (some may be listed
-                    # by other sequences that share a longer prefix of the old row - those keep them)
-                    self._truncate_blocks(src, P // self.args.block_size)
-                    if not self._admit_blocks(r):
-                        self._drop_blocks(src)
-                        self.free.append(src)
-                        r.slot = -1
-                        with self._cv:
-                            self.waiting.appendleft(r)
-                        break
-            else:
-                r.slot = self._take_slot(keep=src)
-                if self.paged:
-                    if not self._admit_blocks(r, src if P > 0 else -1, P):
-                        self.free.append(r.slot)
-                        r.slot = -1
-                        with self._cv:
-                            self.waiting.appendleft(r)
-                        break
-                    if P > 0:
-                        self._share_prefix(src, r.slot, P)               # both table rows list the prefix's physical blocks
-                elif P > 0:
-                    self.gen.copy_prefix(self.cache, src, r.slot, P)     # the prefix belongs to a running sequence: copy its K/V
-            r.prefilled = r.cached_tokens = P
+            if not self._admit_on_prefix(r, src, P):
+                with self._cv:
+                    self.waiting.appendleft(r)
+                break
             self.prefilling.append(r)
             budget -= self._prefill_piece(r, budget)
         if batch:
@@ -725,3 +750,110 @@ class LLMEngine:
         toks = self._sample(logits, reqs)
         self.running = [r for r, t in zip(reqs, toks) if not self._emit(r, t)]
         self.metrics.steps += 1
+
+    # ------------------------------------------------------------------ ragged models: one mixed batch per iteration
+    def _step_ragged(self) -> None:
+        """Scheduler iteration for models with a ragged step: the next token of every running sequence, the next piece of
+        every partly prefilled prompt and the first piece of every admission go through the model as ONE batch. A prompt
+        piece is any length (no padding, no alignment); ``max_prefill_tokens`` bounds the prompt tokens of the iteration."""
+        for r in [r for r in self.running + self.prefilling if r.aborted]:
+            (self.running if r in self.running else self.prefilling).remove(r)
+            self._finish(r, "abort")
+        budget = self.args.max_prefill_tokens
+        chunked = self.args.enable_chunked_prefill
+        while self.waiting and self._slots_available() and budget > 0 and len(self.prefilling) < self.args.max_prefill_per_step:
+            with self._cv:
+                r = self.waiting[0]
+                L = len(r.prompt_ids)
+                if not chunked and L > budget and self.prefilling:
+                    break
+                self.waiting.popleft()
+            src, P = self._lookup_prefix(r.prompt_ids) if self.args.enable_prefix_caching else (-1, 0)
+            if not self._admit_on_prefix(r, src, P):
+                with self._cv:
+                    self.waiting.appendleft(r)              # the pool cannot promise its blocks yet: retry next iteration
+                break
+            with self.metrics.lock:
+                if not getattr(r, "_queued_counted", False):
+                    r._queued_counted = True
+                    self.metrics.queue_sum += time.perf_counter() - r.arrival
+                    self.metrics.queue_count += 1
+                self.metrics.prefix_queries += L
+                self.metrics.prefix_hits += P
+            self.prefilling.append(r)
+            budget -= (L - P) if not chunked else min(L - P, budget)
+        entries, owners = [], []
+        for r in self.running:
+            n = len(r.prompt_ids) + len(r.output_ids)
+            self._grow(r, n)
+            entries.append((r.slot, n - 1, [r.output_ids[-1]], [0]))
+            owners.append(r)
+        budget = self.args.max_prefill_tokens
+        for r in self.prefilling:
+            L = len(r.prompt_ids)
+            n = L - r.prefilled
+            if chunked:
+                n = min(n, max(budget, 0))
+            if n <= 0:
+                continue
+            budget -= n
+            self._grow(r, r.prefilled + n)
+            last = r.prefilled + n >= L
+            entries.append((r.slot, r.prefilled, r.prompt_ids[r.prefilled:r.prefilled + n], [n - 1] if last else []))
+            r.prefilled += n
+            with self.metrics.lock:
+                self.metrics.prompt_tokens += n
+            if last:
+                owners.append(r)
+        if not entries:
+            return
+        logits = self.gen.step(entries, self.cache)
+        if owners:
+            toks = self._sample(logits, owners)
+            for r, t in zip(owners, toks):
+                was_running = r in self.running
+                if not was_running:
+                    self.prefilling.remove(r)
+                if self._emit(r, t):
+                    if was_running:
+                        self.running.remove(r)
+                elif not was_running:
+                    self._start_running(r)
+        self.metrics.steps += 1
+
+    # ------------------------------------------------------------------ replaying given tokens (no sampling)
+    @torch.no_grad()
+    def replay_step(self, entries, end=()) -> Optional[torch.Tensor]:
+        """Teacher-forced step on the engine's own slots, block pool and model step: ``entries`` is a list of
+        ``(request id, tokens, wanted)`` — the next tokens of each request (any mix of prompt pieces and single tokens; a
+        request is admitted at its first entry) and the indices among them whose logits are returned, fp32 [n_wanted, vocab]
+        in entry order (None if nothing is wanted). Requests named in ``end`` give their row and blocks back afterwards.
+        Used to score given continuations and to replay recorded traffic; ragged models only."""
+        if not self.ragged:
+            raise NotImplementedError("replay_step needs a model with a ragged step")
+        live = self.__dict__.setdefault("_replay", {})
+        batch = []
+        for rid, toks, want in entries:
+            r = live.get(rid)
+            if r is None:
+                r = live[rid] = Request(next(self._ids), [], GenerationConfig(max_new_tokens=0))
+                r.slot = self._take_slot()
+                if r.slot < 0:
+                    raise RuntimeError("no free sequence slot")
+            n0 = len(r.prompt_ids)
+            r.prompt_ids.extend(int(t) for t in toks)
+            need = self._nblocks(len(r.prompt_ids)) - len(self._slot_blocks.get(r.slot, []))
+            if need > self._blocks_free():
+                self._evict_cached_rows(need, keep=r.slot)
+            if need > self._blocks_free():
+                raise RuntimeError("KV block pool exhausted")
+            self._grow(r, len(r.prompt_ids))
+            batch.append((r.slot, n0, list(toks), list(want)))
+        logits = self.gen.step(batch, self.cache)
+        for rid in end:
+            r = live.pop(rid, None)
+            if r is not None:
+                r.prefilled = len(r.prompt_ids)
+                r.finish_reason = "replay"
+                self._release_slot(r)
+        return logits
