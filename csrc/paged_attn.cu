@@ -228,6 +228,198 @@ __global__ void paged_attn_merge_kernel(const float* __restrict__ part, const fl
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// prompt pieces on the tensor cores (bf16): 64 query rows x 64 keys per iteration, 4 warps of 16 rows
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kTQ = 64, kTK = 64;
+
+// tiles: [n_tiles, 4] = (first row in the batch, rows, position of the first row, cache row)
+template <int DK>                                     // head size = 16 * DK
+__global__ void __launch_bounds__(128)
+paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ ck,
+                      const __nv_bfloat16* __restrict__ cv, const int* __restrict__ tiles, const int* __restrict__ table,
+                      int max_blocks, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int H, int G,
+                      int block_size, float scale) {
+  constexpr int D = 16 * DK;
+  constexpr int LD = D + 8;                           // padded row (elements): ldmatrix rows land in different banks
+  constexpr int CH = D / 8;                           // 16-byte chunks per row
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][LD]
+  __nv_bfloat16* sk = sq + kTQ * LD;                                          // [2][64][LD]
+  __nv_bfloat16* sv = sk + 2 * kTK * LD;                                      // [2][64][LD]
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int g = h / (H / G);
+  const int row0 = tiles[tile * 4], nrows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], slot = tiles[tile * 4 + 3];
+  const int* trow = table + (long long)slot * max_blocks;
+  const int kv_len = pos0 + nrows;
+  const int nkb = (kv_len + kTK - 1) / kTK;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  auto load_kv = [&](int buf, int kb) {
+    __nv_bfloat16* dk = sk + buf * kTK * LD;
+    __nv_bfloat16* dv = sv + buf * kTK * LD;
+    for (int c = tid; c < kTK * CH; c += 128) {
+      const int r = c / CH, col = (c % CH) * 8;
+      const int kp = kb * kTK + r;
+      if (kp < kv_len) {
+        const long long off = (((long long)trow[kp / block_size] * G + g) * block_size + kp % block_size) * D + col;
+        cp_async16(smem_u32(dk + r * LD + col), ck + off);
+        cp_async16(smem_u32(dv + r * LD + col), cv + off);
+      } else {
+        *reinterpret_cast<uint4*>(dk + r * LD + col) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + r * LD + col) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+
+  for (int c = tid; c < kTQ * CH; c += 128) {
+    const int r = c / CH, col = (c % CH) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < nrows) v = *reinterpret_cast<const uint4*>(q + (long long)(row0 + r) * q_stride + (long long)h * D + col);
+    *reinterpret_cast<uint4*>(sq + r * LD + col) = v;
+  }
+  load_kv(0, 0);
+  cp_async_commit();
+  __syncthreads();
+
+  // Q fragments of this warp's 16 rows: DK k-steps of m16k16
+  uint32_t qa[DK][4];
+  {
+    const int r = warp * 16 + (lane & 15);
+    const int cofs = (lane >> 4) * 8;
+#pragma unroll
+    for (int k = 0; k < DK; ++k) ldsm_x4(smem_u32(sq + r * LD + k * 16 + cofs), qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
+  }
+
+  const float LOG2E = 1.4426950408889634f;
+  const float sl2 = scale * LOG2E;
+  const float sink2 = sinks ? sinks[h] * LOG2E : -INFINITY;
+  float m0 = sink2, m1 = sink2, l0 = 0.f, l1 = 0.f;
+  float o[2 * DK][4];
+#pragma unroll
+  for (int i = 0; i < 2 * DK; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int qpos0 = pos0 + warp * 16 + (lane >> 2);    // position of this thread's first row; the second is + 8
+
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) load_kv(buf ^ 1, kb + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* bk = sk + buf * kTK * LD;
+    const __nv_bfloat16* bv = sv + buf * kTK * LD;
+
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < DK; ++k) {
+        uint32_t b0, b1;
+        ldsm_x2(smem_u32(bk + (n * 8 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8), b0, b1);
+        mma_bf16_16816(s[n], qa[k][0], qa[k][1], qa[k][2], qa[k][3], b0, b1);
+      }
+    }
+    // scale, causal mask, running max
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+    const int kbase = kb * kTK + 2 * (lane & 3);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kp = kbase + n * 8 + (j & 1);
+        const int qp = qpos0 + (j >> 1) * 8;
+        const float v = kp <= qp ? s[n][j] * sl2 : -INFINITY;
+        s[n][j] = v;
+        if (j >> 1) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float e0 = mn0 == -INFINITY ? 0.f : mn0, e1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float r0 = exp2f(m0 - e0), r1 = exp2f(m1 - e1);      // exp2(-inf) = 0 when nothing was seen yet
+    m0 = mn0; m1 = mn1;
+    l0 *= r0; l1 *= r1;
+#pragma unroll
+    for (int i = 0; i < 2 * DK; ++i) { o[i][0] *= r0; o[i][1] *= r0; o[i][2] *= r1; o[i][3] *= r1; }
+    uint32_t pa[4][4];                                  // P as A fragments: 4 k-steps of 16 keys
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float p0 = exp2f(s[n][0] - e0), p1 = exp2f(s[n][1] - e0), p2 = exp2f(s[n][2] - e1), p3 = exp2f(s[n][3] - e1);
+      // the sums use the probabilities as they are multiplied (rounded to bf16), so numerator and denominator agree
+      const uint32_t lo = pack_bf16x2(p0, p1), hi = pack_bf16x2(p2, p3);
+      const float2 flo = unpack_bf16x2(lo), fhi = unpack_bf16x2(hi);
+      l0 += flo.x + flo.y;
+      l1 += fhi.x + fhi.y;
+      pa[n >> 1][(n & 1) * 2] = lo;
+      pa[n >> 1][(n & 1) * 2 + 1] = hi;
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int n = 0; n < 2 * DK; ++n) {
+        uint32_t b0, b1;
+        ldsm_x2_trans(smem_u32(bv + (kk * 16 + (lane & 15)) * LD + n * 8), b0, b1);
+        mma_bf16_16816(o[n], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+      }
+    }
+    __syncthreads();                                    // everyone is done with `buf` before the next prefetch lands in it
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (sinks) { l0 += exp2f(sink2 - m0); l1 += exp2f(sink2 - m1); }
+  const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
+#pragma unroll
+  for (int n = 0; n < 2 * DK; ++n) {
+    const int d = n * 8 + 2 * (lane & 3);
+    if (ra < nrows)
+      *reinterpret_cast<uint32_t*>(out + ((long long)(row0 + ra) * H + h) * D + d) = pack_bf16x2(o[n][0] * i0, o[n][1] * i0);
+    if (rb < nrows)
+      *reinterpret_cast<uint32_t*>(out + ((long long)(row0 + rb) * H + h) * D + d) = pack_bf16x2(o[n][2] * i1, o[n][3] * i1);
+  }
+}
+
+template <int DK>
+static int launch_mma(const void* q, long long q_stride, const void* ck, const void* cv, const int* tiles, int n_tiles,
+                      const int* table, int max_blocks, const float* sinks, void* out, int H, int G, int block_size, float scale,
+                      cudaStream_t st) {
+  constexpr int LD = 16 * DK + 8;
+  const size_t smem = (size_t)(kTQ + 4 * kTK) * LD * sizeof(__nv_bfloat16);
+  auto kern = paged_attn_mma_kernel<DK>;
+  if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(n_tiles, H), 128, smem, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)ck, (const __nv_bfloat16*)cv,
+                                             tiles, table, max_blocks, sinks, (__nv_bfloat16*)out, H, G, block_size, scale);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -277,4 +469,18 @@ B200_API int b200_paged_attn(const void* q, long long q_stride, const void* ck, 
 #undef ATTN_LAUNCH
   B200_LAUNCH_CHECK();
   return 0;
+}
+
+B200_API int b200_paged_attn_mma(const void* q, long long q_stride, const void* ck, const void* cv, const void* tiles, int n_tiles,
+                                 const void* table, int max_blocks, const void* sinks, void* out, int H, int G, int D,
+                                 int block_size, float scale, int dtype, void* stream_) {
+  cudaStream_t st = (cudaStream_t)stream_;
+  if (n_tiles <= 0) return 0;
+  if (dtype != B200_DT_BF16 || D % 16 || D < 16 || D > 128) return B200_ERR_UNSUPPORTED;
+  if (H <= 0 || G <= 0 || H % G || block_size <= 0 || (q_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15)) return B200_ERR_BAD_SHAPE;
+#define MMA(DK) case DK: return launch_mma<DK>(q, q_stride, ck, cv, (const int*)tiles, n_tiles, (const int*)table, max_blocks, \
+                                                (const float*)sinks, out, H, G, block_size, scale, st)
+  switch (D / 16) { MMA(1); MMA(2); MMA(3); MMA(4); MMA(5); MMA(6); MMA(7); MMA(8); }
+#undef MMA
+  return B200_ERR_UNSUPPORTED;
 }

@@ -27,13 +27,12 @@ class Pieces:
     """Runs of consecutive tokens of one sequence inside a step, cut into tiles of at most ``TILE_Q`` query rows:
     ``tiles`` int32 [n_tiles, 4] = (first row in the batch, rows, position of the first row, cache row)."""
     tiles: torch.Tensor
-    slot_of_tile: torch.Tensor
     n_tiles: int
     longest: int                    # tokens of the longest run
 
     def use_mma(self, q: torch.Tensor, head_dim: int, window: int) -> bool:
         import os
-        return (self.longest >= 8 and q.dtype in (torch.bfloat16, torch.float16) and head_dim % 16 == 0 and head_dim <= 128
+        return (self.longest >= 8 and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and window == 0 and os.environ.get("B200_PAGED_MMA", "1") != "0")
 
 
@@ -97,7 +96,7 @@ class RaggedGenerator(Generator):
         else:
             ids_t = torch.tensor(ids, dtype=torch.long)
             tl = torch.tensor(tiles, dtype=torch.int32)
-        pieces = Pieces(tl, tl[:, 3].contiguous(), len(tiles), longest)
+        pieces = Pieces(tl, len(tiles), longest)
         want_t = torch.tensor(want, dtype=torch.long, device=dev) if want else torch.zeros(1, dtype=torch.long, device=dev)
         logits = self.model.forward_ragged(ids_t, meta[0], meta[1], cache, want_t, max_pos=max_pos, pieces=pieces,
                                            layer_outputs=layer_outputs)
