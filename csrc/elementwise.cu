@@ -531,21 +531,33 @@ B200_API int b200_fold_grad(void* x, float* y, long long n, float scale, int cle
 // Logit soft cap, in place on fp32:  x <- cap * tanh(x / cap)
 // ---------------------------------------------------------------------------------------------
 namespace b200 {
-template <typename T>
+template <typename T, int V>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha,
                                    float shift) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (idx >= rows * F) return;
   const long long r = idx / F;
   const int c = (int)(idx - r * F);
-  float g = to_f32<T>(gu[r * 2 * F + c]);
-  float u = to_f32<T>(gu[r * 2 * F + F + c]);
-  if (limit > 0.f) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
+  T gv[V], uv[V], ov[V];
+  if (V > 1) {
+    *reinterpret_cast<uint4*>(gv) = *reinterpret_cast<const uint4*>(gu + r * 2 * F + c);
+    *reinterpret_cast<uint4*>(uv) = *reinterpret_cast<const uint4*>(gu + r * 2 * F + F + c);
+  } else {
+    gv[0] = gu[r * 2 * F + c];
+    uv[0] = gu[r * 2 * F + F + c];
   }
-  const float sig = 1.f / (1.f + expf(-alpha * g));
-  y[idx] = from_f32<T>(g * sig * (u + shift));
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    float g = to_f32<T>(gv[j]), u = to_f32<T>(uv[j]);
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+    }
+    const float sig = 1.f / (1.f + expf(-alpha * g));
+    ov[j] = from_f32<T>(g * sig * (u + shift));
+  }
+  if (V > 1) *reinterpret_cast<uint4*>(y + idx) = *reinterpret_cast<const uint4*>(ov);
+  else y[idx] = ov[0];
 }
 
 __global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
@@ -559,8 +571,15 @@ B200_API int b200_clamped_glu(const void* gu, void* y, long long rows, int F, fl
   using namespace b200;
   if (rows <= 0 || F <= 0) return rows == 0 ? 0 : B200_ERR_BAD_SHAPE;
   const int tb = 256;
-  const unsigned grid = (unsigned)((rows * F + tb - 1) / tb);
-  B200_DISPATCH_T(dtype, clamped_glu_kernel<T><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift));
+  const int V = dtype == B200_DT_FP32 ? 4 : 8;
+  const bool vec = F % V == 0 && !((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15);
+  if (vec) {
+    const unsigned grid = (unsigned)((rows * F / V + tb - 1) / tb);
+    B200_DISPATCH_T(dtype, clamped_glu_kernel<T, 16 / sizeof(T)><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift));
+  } else {
+    const unsigned grid = (unsigned)((rows * F + tb - 1) / tb);
+    B200_DISPATCH_T(dtype, clamped_glu_kernel<T, 1><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift));
+  }
   B200_LAUNCH_CHECK();
   return 0;
 }

@@ -9,10 +9,11 @@
 //   b200_rope_paged_store   rotary embedding on q (in place) and k, k -> cache K; the value rows come either from a v
 //                           section of the projection or (v_from_k) are the keys as projected, before rotation.
 //                           Pairs are interleaved (2i, 2i+1) or split (i, i + rot/2); only the first `rot` dims turn.
-//   b200_paged_attn         one warp per (token, query head): keys are walked 32 at a time (one key per lane for the
-//                           scores, one output column set per lane for P V), online softmax in fp32, any head size up
-//                           to 256, 16-bit or 32-bit cache. `nsplit` > 1 cuts the keys of every token into that many
-//                           ranges (long-context decode) and a second kernel merges the partial (max, sum, acc) triples.
+//   b200_paged_attn         per-token attention in fp32 arithmetic over a 16-bit or 32-bit cache, any head size up to 256:
+//                           a vector kernel (16-byte row chunks, the query heads of a KV group share the K/V reads) and a
+//                           scalar one for head sizes that are not whole chunks. `nsplit` > 1 cuts the keys of every token
+//                           into that many ranges (long-context decode); a second kernel merges the partial
+//                           (max, sum, acc) triples.
 //   b200_paged_attn_mma     16-bit prompt pieces on the tensor cores (mma.sync m16n8k16): 64 query rows of one piece per
 //                           CTA, one cache page (or 64 keys of it) per iteration.
 //
@@ -201,6 +202,136 @@ paged_attn_kernel(const T* __restrict__ q, long long q_stride, const T* __restri
         const int d = lane + 32 * i;
         if (d < D) pr[2 + d] = acc[i];
       }
+    }
+  }
+}
+
+// Vector variant (head size a multiple of one 16-byte chunk, at most 32 chunks): a CTA owns one token, up to HB query heads
+// of one KV group and one key range. A lane is (key sub-index, chunk): the CP lanes of a group read one K row and the same V
+// row with one 16-byte load each, so a warp instruction covers 32 / CP whole rows; the score is reduced over the group's
+// lanes, and every lane keeps its own running (max, sum, acc) for the keys it has seen — nothing crosses groups inside the
+// loop. Groups are merged by shuffles at the end, the four warps through shared memory.
+template <typename T, int HB>
+__global__ void __launch_bounds__(128)
+paged_attn_vec_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ ck, const T* __restrict__ cv,
+                      const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ table, int max_blocks,
+                      const float* __restrict__ sinks, T* __restrict__ out, float* __restrict__ part, int H, int G, int D,
+                      int bs_log2, float scale, int window, int nsplit, int CP, int CPR) {
+  constexpr int E = 16 / sizeof(T);                    // elements per chunk
+  extern __shared__ float sm[];                        // [4 warps][HB][D + 2]
+  const int t = blockIdx.x;
+  const int rep = H / G;
+  const int passes = (rep + HB - 1) / HB;
+  const int g = blockIdx.y / passes;
+  const int h0 = g * rep + (blockIdx.y % passes) * HB;
+  const int nh = min(HB, g * rep + rep - h0);
+  const int split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KPI = 32 / CP;                             // keys per warp instruction
+  const int kk = lane / CP, c = lane % CP;
+  const bool live = c < CPR;
+  const int p = pos[t];
+  const int* trow = table + (long long)slot[t] * max_blocks;
+  int k_lo = 0, k_hi = p + 1;
+  if (window > 0 && p + 1 - window > 0) k_lo = p + 1 - window;
+  if (nsplit > 1) {
+    const int span = k_hi - k_lo;
+    const int chunk = ((span + nsplit - 1) / nsplit + 31) / 32 * 32;
+    k_lo = k_lo + split * chunk;
+    k_hi = min(k_hi, k_lo + chunk);
+  }
+  float qv[HB][E], acc[HB][E], m[HB], l[HB];
+#pragma unroll
+  for (int hh = 0; hh < HB; ++hh) {
+    m[hh] = -INFINITY;
+    l[hh] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      acc[hh][e] = 0.f;
+      qv[hh][e] = (live && hh < nh) ? to_f32<T>(q[(long long)t * q_stride + (long long)(h0 + hh) * D + c * E + e]) * scale : 0.f;
+    }
+  }
+  const int bs_mask = (1 << bs_log2) - 1;
+  const int stride = 4 * KPI;
+  for (int k0 = k_lo + warp * KPI + kk; k0 - kk - warp * KPI < k_hi; k0 += stride) {
+    const bool valid = k0 < k_hi;
+    float kf[E], vf[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) kf[e] = vf[e] = 0.f;
+    if (valid && live) {
+      const long long off = ((((long long)trow[k0 >> bs_log2] * G + g) << bs_log2) + (k0 & bs_mask)) * D + c * E;
+      const uint4 kr = *reinterpret_cast<const uint4*>(ck + off);
+      const uint4 vr = *reinterpret_cast<const uint4*>(cv + off);
+      const T* kp = reinterpret_cast<const T*>(&kr);
+      const T* vp = reinterpret_cast<const T*>(&vr);
+#pragma unroll
+      for (int e = 0; e < E; ++e) { kf[e] = to_f32<T>(kp[e]); vf[e] = to_f32<T>(vp[e]); }
+    }
+#pragma unroll
+    for (int hh = 0; hh < HB; ++hh) {
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) s = fmaf(qv[hh][e], kf[e], s);
+      for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (valid) {
+        const float mn = fmaxf(m[hh], s);
+        const float r = expf(m[hh] - mn);             // 0 on the first key (m = -inf)
+        const float pj = expf(s - mn);
+        m[hh] = mn;
+        l[hh] = l[hh] * r + pj;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(pj, vf[e], acc[hh][e] * r);
+      }
+    }
+  }
+  // merge the key groups of the warp
+#pragma unroll
+  for (int hh = 0; hh < HB; ++hh) {
+    for (int o = CP; o < 32; o <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[hh], o);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[hh], o);
+      const float mn = fmaxf(m[hh], m2);
+      const float e1 = m[hh] == -INFINITY ? 0.f : expf(m[hh] - mn);
+      const float e2 = m2 == -INFINITY ? 0.f : expf(m2 - mn);
+      l[hh] = l[hh] * e1 + l2 * e2;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, acc[hh][e], o);
+        acc[hh][e] = acc[hh][e] * e1 + a2 * e2;
+      }
+      m[hh] = mn;
+    }
+    if (kk == 0 && live) {
+      float* w = sm + (warp * HB + hh) * (D + 2);
+      if (c == 0) { w[0] = m[hh]; w[1] = l[hh]; }
+#pragma unroll
+      for (int e = 0; e < E; ++e) w[2 + c * E + e] = acc[hh][e];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+    const int hh = i / D, d = i % D;
+    const int h = h0 + hh;
+    const bool own_sink = sinks != nullptr && nsplit == 1;
+    float mt = own_sink ? sinks[h] : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm[(w * HB + hh) * (D + 2)]);
+    float lt = own_sink ? expf(sinks[h] - mt) : 0.f, at = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* ws = sm + (w * HB + hh) * (D + 2);
+      if (ws[0] != -INFINITY) {
+        const float e = expf(ws[0] - mt);
+        lt += ws[1] * e;
+        at += ws[2 + d] * e;
+      }
+    }
+    if (nsplit == 1) {
+      out[((long long)t * H + h) * D + d] = from_f32<T>(lt > 0.f ? at / lt : 0.f);
+    } else {
+      float* pr = part + (((long long)t * H + h) * nsplit + split) * (D + 2);
+      if (d == 0) { pr[0] = mt; pr[1] = lt; }
+      pr[2 + d] = at;
     }
   }
 }
@@ -451,6 +582,39 @@ B200_API int b200_paged_attn(const void* q, long long q_stride, const void* ck, 
   if (H <= 0 || G <= 0 || H % G || D <= 0 || D > kMaxD || block_size <= 0 || nsplit < 1) return B200_ERR_BAD_SHAPE;
   if (nsplit > 1 && !part) return B200_ERR_BAD_SHAPE;
   const int rep = H / G;
+  {
+    // vector kernel: rows of whole 16-byte chunks, at most 32 of them, pages of a power-of-two size
+    const int E = dtype == B200_DT_FP32 ? 4 : 8;
+    const int CPR = D / E;
+    int bs_log2 = 0;
+    while ((1 << bs_log2) < block_size) ++bs_log2;
+    if (D % E == 0 && CPR <= 32 && (1 << bs_log2) == block_size && q_stride % E == 0 && !(reinterpret_cast<uintptr_t>(q) & 15)) {
+      int CP = 1;
+      while (CP < CPR) CP <<= 1;
+      const int HB = rep >= 4 ? 4 : (rep >= 2 ? 2 : 1);
+      const int passes = (rep + HB - 1) / HB;
+      dim3 vgrid(tokens, G * passes, nsplit);
+      const size_t vsmem = (size_t)4 * HB * (D + 2) * sizeof(float);
+#define VEC_LAUNCH(T, HBV)                                                                                                     \
+  paged_attn_vec_kernel<T, HBV><<<vgrid, 128, vsmem, st>>>((const T*)q, q_stride, (const T*)ck, (const T*)cv, (const int*)pos,  \
+                                                           (const int*)slot, (const int*)table, max_blocks, (const float*)sinks, \
+                                                           (T*)out, (float*)part, H, G, D, bs_log2, scale, window, nsplit, CP, CPR)
+#define VEC_DISPATCH(T)                                                                                                        \
+  do {                                                                                                                         \
+    if (HB == 4) VEC_LAUNCH(T, 4); else if (HB == 2) VEC_LAUNCH(T, 2); else VEC_LAUNCH(T, 1);                                  \
+    if (nsplit > 1)                                                                                                            \
+      paged_attn_merge_kernel<T><<<dim3(tokens, H), 64, 0, st>>>((const float*)part, (const float*)sinks, (T*)out, H, D, nsplit); \
+  } while (0)
+      if (dtype == B200_DT_BF16) VEC_DISPATCH(__nv_bfloat16);
+      else if (dtype == B200_DT_FP16) VEC_DISPATCH(__half);
+      else if (dtype == B200_DT_FP32) VEC_DISPATCH(float);
+      else return B200_ERR_UNSUPPORTED;
+#undef VEC_DISPATCH
+#undef VEC_LAUNCH
+      B200_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   const int warps = rep < 8 ? rep : 8;
   dim3 grid(tokens, G, nsplit), block(32 * warps);
   const size_t smem = (size_t)warps * D * sizeof(float);

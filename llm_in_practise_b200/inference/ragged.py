@@ -12,10 +12,13 @@ Deployment/Ray/serve_run_examples/deepseek.py:29-34).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
 import torch
+
+from ..ops.gemm import ensure_graph_workspace
 
 from .generate import GenerationConfig, Generator, PagedKVCache, sample_next
 
@@ -44,6 +47,7 @@ class RaggedGenerator(Generator):
 
     def __init__(self, model, tokenizer=None, max_len: int = 4096):
         super().__init__(model, tokenizer, max_len)
+        self._graph_decode = os.environ.get("B200_RAGGED_GRAPH", "1") != "0"
 
     # ------------------------------------------------------------------ cache
     def make_cache(self, num_blocks: int, block_size: int, max_seqs: int, max_len: int) -> PagedKVCache:
@@ -51,8 +55,10 @@ class RaggedGenerator(Generator):
         is left to unset table entries; callers hand out blocks 1 .. num_blocks."""
         m = self.model
         lay = m.kv_layout()
-        return PagedKVCache(len(lay), num_blocks + 1, [g for g, _ in lay], block_size, [d for _, d in lay], m.embed_tokens.dtype,
-                            m.embed_tokens.device, max_seqs, max_len)
+        cache = PagedKVCache(len(lay), num_blocks + 1, [g for g, _ in lay], block_size, [d for _, d in lay], m.embed_tokens.dtype,
+                             m.embed_tokens.device, max_seqs + 1, max_len)
+        cache.scratch_row = max_seqs             # a row that never gets blocks: padding tokens of a bucketed batch write to block 0
+        return cache
 
     def kv_token_bytes(self) -> int:
         es = self.model.embed_tokens.element_size()
@@ -65,6 +71,9 @@ class RaggedGenerator(Generator):
         write. Returns the fp32 logits of the wanted tokens in entry order [n_wanted, vocab], or None if nothing is wanted
         (the K/V of the tokens are stored all the same)."""
         dev = self.model.embed_tokens.device
+        if (dev.type == "cuda" and layer_outputs is None and self._graph_decode and entries
+                and all(len(e[2]) == 1 and list(e[3]) == [0] for e in entries)):
+            return self.decode([e[2][0] for e in entries], [e[1] for e in entries], [e[0] for e in entries], cache)
         ids: List[int] = []
         pos: List[int] = []
         slot: List[int] = []
@@ -101,6 +110,46 @@ class RaggedGenerator(Generator):
         logits = self.model.forward_ragged(ids_t, meta[0], meta[1], cache, want_t, max_pos=max_pos, pieces=pieces,
                                            layer_outputs=layer_outputs)
         return logits if want else None
+
+    @torch.no_grad()
+    def decode(self, tokens: Sequence[int], positions: Sequence[int], rows: Sequence[int], cache: PagedKVCache) -> torch.Tensor:
+        """One token per sequence (``tokens[i]`` at ``positions[i]`` of cache row ``rows[i]``), replayed from a CUDA graph: a
+        decode step is ~10 short launches per layer, so eager execution is bound by the launch rate. One graph per
+        (batch bucket, context bucket, cache); token ids, positions and rows are read from device tensors, padding rows of
+        the bucket write to the cache's scratch row. Returns fp32 logits [len(tokens), vocab]."""
+        dev = self.model.embed_tokens.device
+        n = len(tokens)
+        nb = 1
+        while nb < n:
+            nb *= 2
+        mp = 64
+        while mp < max(positions) + 1:
+            mp *= 2
+        mp = min(mp, cache.max_len)
+        pad = nb - n
+        host = torch.tensor([list(tokens) + [0] * pad, list(positions) + [0] * pad, list(rows) + [cache.scratch_row] * pad], dtype=torch.int64)
+        # the graphs live on the cache they were captured against (they hold its addresses): they go when it goes, and a new
+        # cache that happens to get the old one's id() cannot pick them up
+        graphs = cache.__dict__.setdefault("_decode_graphs", {})
+        key = (nb, mp)
+        g = graphs.get(key)
+        if g is None:
+            st = {"ids": torch.zeros(nb, dtype=torch.long, device=dev), "pos": torch.zeros(nb, dtype=torch.int32, device=dev),
+                  "slot": torch.full((nb,), cache.scratch_row, dtype=torch.int32, device=dev)}
+            ensure_graph_workspace(dev)
+            self.model.forward_ragged(st["ids"], st["pos"], st["slot"], cache, None, max_pos=mp - 1)       # warm-up: lazily built buffers
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                st["logits"] = self.model.forward_ragged(st["ids"], st["pos"], st["slot"], cache, None, max_pos=mp - 1)
+            g = graphs[key] = (graph, st)
+        graph, st = g
+        hd = host.pin_memory().to(dev, non_blocking=True)
+        st["ids"].copy_(hd[0])
+        st["pos"].copy_(hd[1])
+        st["slot"].copy_(hd[2])
+        graph.replay()
+        return st["logits"][:n].clone()          # the graph's output buffer is rewritten by the next replay
 
     # ------------------------------------------------------------------ single-process generation
     def _generate(self, input_ids: torch.Tensor, config: Optional[GenerationConfig], streamer, seed: Optional[int],

@@ -151,7 +151,7 @@ class LLMEngine:
             # physical block 0 is never handed out: table entries that were never set (the scratch row, positions a padded
             # prefill piece writes past a sequence's end) point at it
             if self.ragged:
-                self.cache = self.gen.make_cache(nb, BS, self.args.max_num_seqs + 1, self.args.max_model_len)
+                self.cache = self.gen.make_cache(nb, BS, self.args.max_num_seqs, self.args.max_model_len)
             else:
                 self.cache = PagedKVCache(c.num_hidden_layers, nb + 1, c.num_key_value_heads, BS, c.head_dim,
                                           self.model.embed_tokens.dtype, self.device, self.args.max_num_seqs + 1, self.args.max_model_len)
