@@ -79,6 +79,17 @@ VARIANTS = {
 }
 
 
+SC2 = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 128}
+# sizes that are not multiples of the kernels' vector widths: width % 8 != 0 (no TMA rows), odd vocabulary, head sizes that
+# are not whole 16-byte chunks, 3 / 5 / 10 heads, 7 experts
+ODD = {
+    "w72": lambda: O.make_config(72, 75, [O.attn_layer(3, 1, 40, 10, 1e4, SC2, mlp=O.dense(100, 1.5)),
+                                          O.attn_layer(3, 1, 40, 10, 1e4, SC2, mlp=O.moe(3, 2, 36))]),
+    "w100": lambda: O.make_config(100, 130, [O.attn_layer(5, 5, 36, 36, 1e6, None, mlp=O.moe(7, 3, 52)),
+                                             O.attn_layer(10, 2, 20, 2, 1e6, None, mlp=O.dense(90, 9.0))], softcap=50.0),
+}
+
+
 # ------------------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ------------------------------------------------------------------------------------------------------------------
@@ -347,6 +358,25 @@ def test_whole_prompt_and_residuals(tmp_path, device, dtype, variant):
     one = gen.step([(0, 0, toks[:1], [0])], fresh_cache(gen, 1, 64))
     assert rel_err(one, ref[:1]) < 2 * tol(dtype)
     assert rel_err(got[:3], ref[:3]) < 2 * tol(dtype)
+
+
+@pytest.mark.parametrize("device,dtype", CASES)
+@pytest.mark.parametrize("name", list(ODD))
+def test_odd_sizes(tmp_path, device, dtype, name):
+    from llm_in_practise_b200.inference.ragged import RaggedGenerator
+    cfg = ODD[name]()
+    W = O.random_weights(cfg, seed=3)
+    model = build(tmp_path, cfg, W, device, dtype)
+    n = 140
+    toks = _tokens(n, cfg["vocab"], 2)
+    ref = O.forward(cfg, W, toks)
+    gen = RaggedGenerator(model, None, 192)
+    cache = fresh_cache(gen, 2, 192)
+    p, outs = 0, []
+    for c in [30, 34, 2, 3, 61, 1, 1, 1, 7]:
+        outs.append(gen.step([(1, p, toks[p:p + c], list(range(c)))], cache))
+        p += c
+    assert_rows(torch.cat(outs, 0), ref, dtype, name)
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
