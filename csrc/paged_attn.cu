@@ -253,34 +253,45 @@ paged_attn_vec_kernel(const T* __restrict__ q, long long q_stride, const T* __re
   }
   const int bs_mask = (1 << bs_log2) - 1;
   const int stride = 4 * KPI;
-  for (int k0 = k_lo + warp * KPI + kk; k0 - kk - warp * KPI < k_hi; k0 += stride) {
-    const bool valid = k0 < k_hi;
-    float kf[E], vf[E];
+  constexpr int U = HB >= 4 ? 2 : 4;                   // keys in flight per lane: their loads are issued before the first is used
+                                                       // (four heads per lane leave registers for two)
+  for (int kb = k_lo; kb < k_hi; kb += stride * U) {
+    uint4 kr[U], vr[U];
+    bool valid[U];
 #pragma unroll
-    for (int e = 0; e < E; ++e) kf[e] = vf[e] = 0.f;
-    if (valid && live) {
-      const long long off = ((((long long)trow[k0 >> bs_log2] * G + g) << bs_log2) + (k0 & bs_mask)) * D + c * E;
-      const uint4 kr = *reinterpret_cast<const uint4*>(ck + off);
-      const uint4 vr = *reinterpret_cast<const uint4*>(cv + off);
-      const T* kp = reinterpret_cast<const T*>(&kr);
-      const T* vp = reinterpret_cast<const T*>(&vr);
-#pragma unroll
-      for (int e = 0; e < E; ++e) { kf[e] = to_f32<T>(kp[e]); vf[e] = to_f32<T>(vp[e]); }
+    for (int u = 0; u < U; ++u) {
+      const int k0 = kb + u * stride + warp * KPI + kk;
+      valid[u] = k0 < k_hi;
+      kr[u] = vr[u] = make_uint4(0, 0, 0, 0);
+      if (valid[u] && live) {
+        const long long off = ((((long long)trow[k0 >> bs_log2] * G + g) << bs_log2) + (k0 & bs_mask)) * D + c * E;
+        kr[u] = *reinterpret_cast<const uint4*>(ck + off);
+        vr[u] = *reinterpret_cast<const uint4*>(cv + off);
+      }
     }
 #pragma unroll
-    for (int hh = 0; hh < HB; ++hh) {
-      float s = 0.f;
+    for (int u = 0; u < U; ++u) {
+      if (kb + u * stride >= k_hi) break;             // uniform over the CTA: no lane has a key in this or a later slot
+      float kf[E], vf[E];
+      const T* kp = reinterpret_cast<const T*>(&kr[u]);
+      const T* vp = reinterpret_cast<const T*>(&vr[u]);
 #pragma unroll
-      for (int e = 0; e < E; ++e) s = fmaf(qv[hh][e], kf[e], s);
-      for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (valid) {
-        const float mn = fmaxf(m[hh], s);
-        const float r = expf(m[hh] - mn);             // 0 on the first key (m = -inf)
-        const float pj = expf(s - mn);
-        m[hh] = mn;
-        l[hh] = l[hh] * r + pj;
+      for (int e = 0; e < E; ++e) { kf[e] = to_f32<T>(kp[e]); vf[e] = to_f32<T>(vp[e]); }
 #pragma unroll
-        for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(pj, vf[e], acc[hh][e] * r);
+      for (int hh = 0; hh < HB; ++hh) {
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) s = fmaf(qv[hh][e], kf[e], s);
+        for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid[u]) {
+          const float mn = fmaxf(m[hh], s);
+          const float r = expf(m[hh] - mn);           // 0 on the first key (m = -inf)
+          const float pj = expf(s - mn);
+          m[hh] = mn;
+          l[hh] = l[hh] * r + pj;
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(pj, vf[e], acc[hh][e] * r);
+        }
       }
     }
   }
@@ -369,12 +380,12 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r
 __device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
-__device__ __forceinline__ void ldsm_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                                uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -383,23 +394,30 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int kTQ = 64, kTK = 64;
 
 // tiles: [n_tiles, 4] = (first row in the batch, rows, position of the first row, cache row)
 template <int DK>                                     // head size = 16 * DK
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)             // three CTAs per SM: 4 x 17 KB tiles at head size 128, <= 170 registers
 paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ ck,
                       const __nv_bfloat16* __restrict__ cv, const int* __restrict__ tiles, const int* __restrict__ table,
                       int max_blocks, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int H, int G,
-                      int block_size, float scale) {
+                      int bs_log2, float scale) {
   constexpr int D = 16 * DK;
   constexpr int LD = D + 8;                           // padded row (elements): ldmatrix rows land in different banks
   constexpr int CH = D / 8;                           // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][LD]
-  __nv_bfloat16* sk = sq + kTQ * LD;                                          // [2][64][LD]
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [2][64][LD]
   __nv_bfloat16* sv = sk + 2 * kTK * LD;                                      // [2][64][LD]
-  const int tile = blockIdx.x, h = blockIdx.y;
+  __nv_bfloat16* sq = sk + kTK * LD;                                          // Q is staged in K buffer 1 until its fragments are read
+  // later tiles of a piece see more keys: taking them first keeps the long CTAs out of the last wave
+  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int g = h / (H / G);
   const int row0 = tiles[tile * 4], nrows = tiles[tile * 4 + 1], pos0 = tiles[tile * 4 + 2], slot = tiles[tile * 4 + 3];
   const int* trow = table + (long long)slot * max_blocks;
@@ -407,19 +425,27 @@ paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, c
   const int nkb = (kv_len + kTK - 1) / kTK;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // two threads per key row, alternating 16-byte chunks (a pair fills whole 32-byte sectors); one page lookup per row
+  const int bs_mask = (1 << bs_log2) - 1;
   auto load_kv = [&](int buf, int kb) {
-    __nv_bfloat16* dk = sk + buf * kTK * LD;
-    __nv_bfloat16* dv = sv + buf * kTK * LD;
-    for (int c = tid; c < kTK * CH; c += 128) {
-      const int r = c / CH, col = (c % CH) * 8;
-      const int kp = kb * kTK + r;
-      if (kp < kv_len) {
-        const long long off = (((long long)trow[kp / block_size] * G + g) * block_size + kp % block_size) * D + col;
-        cp_async16(smem_u32(dk + r * LD + col), ck + off);
-        cp_async16(smem_u32(dv + r * LD + col), cv + off);
-      } else {
-        *reinterpret_cast<uint4*>(dk + r * LD + col) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + r * LD + col) = make_uint4(0, 0, 0, 0);
+    const int r = tid >> 1, half = tid & 1;
+    const int kp = kb * kTK + r;
+    __nv_bfloat16* dk = sk + (buf * kTK + r) * LD;
+    __nv_bfloat16* dv = sv + (buf * kTK + r) * LD;
+    if (kp < kv_len) {
+      const long long off = ((((long long)trow[kp >> bs_log2] * G + g) << bs_log2) + (kp & bs_mask)) * D;
+#pragma unroll
+      for (int i = 0; i < CH / 2; ++i) {
+        const int col = (half + 2 * i) * 8;
+        cp_async16(smem_u32(dk + col), ck + off + col);
+        cp_async16(smem_u32(dv + col), cv + off + col);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH / 2; ++i) {
+        const int col = (half + 2 * i) * 8;
+        *reinterpret_cast<uint4*>(dk + col) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + col) = make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -442,6 +468,7 @@ paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, c
 #pragma unroll
     for (int k = 0; k < DK; ++k) ldsm_x4(smem_u32(sq + r * LD + k * 16 + cofs), qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
   }
+  __syncthreads();                                      // every warp has its Q fragments: buffer 1 may be refilled with keys
 
   const float LOG2E = 1.4426950408889634f;
   const float sl2 = scale * LOG2E;
@@ -461,38 +488,54 @@ paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, c
     const __nv_bfloat16* bk = sk + buf * kTK * LD;
     const __nv_bfloat16* bv = sv + buf * kTK * LD;
 
+    // S = Q K^T, k-steps outermost: the eight key tiles of a step are independent accumulators, so consecutive MMAs never
+    // wait for each other (tile-outermost would chain the k-steps of one accumulator back to back)
     float s[8][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
-      for (int k = 0; k < DK; ++k) {
-        uint32_t b0, b1;
-        ldsm_x2(smem_u32(bk + (n * 8 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8), b0, b1);
-        mma_bf16_16816(s[n], qa[k][0], qa[k][1], qa[k][2], qa[k][3], b0, b1);
+    for (int k = 0; k + 1 < DK; k += 2) {                // one ldmatrix.x4 feeds two k-steps of a key tile
+      uint32_t b[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+        ldsm_x4(smem_u32(bk + (n * 8 + (lane & 7)) * LD + k * 16 + (lane >> 3) * 8), b[n][0], b[n][1], b[n][2], b[n][3]);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], qa[k][0], qa[k][1], qa[k][2], qa[k][3], b[n][0], b[n][1]);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], qa[k + 1][0], qa[k + 1][1], qa[k + 1][2], qa[k + 1][3], b[n][2], b[n][3]);
+    }
+    if (DK & 1) {
+      constexpr int k = DK - 1;
+      uint32_t b[8][2];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) ldsm_x2(smem_u32(bk + (n * 8 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8), b[n][0], b[n][1]);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], qa[k][0], qa[k][1], qa[k][2], qa[k][3], b[n][0], b[n][1]);
+    }
+    // causal mask (only blocks that reach past this warp's first query position need one), running max on the raw scores,
+    // then p = 2^(s * scale * log2e - max): one FMA and one ex2 per score
+    if (kb * kTK + kTK - 1 > pos0 + warp * 16) {
+      const int kbase = kb * kTK + 2 * (lane & 3);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (kbase + n * 8 + (j & 1) > qpos0 + (j >> 1) * 8) s[n][j] = -INFINITY;
       }
     }
-    // scale, causal mask, running max
     float mx0 = -INFINITY, mx1 = -INFINITY;
-    const int kbase = kb * kTK + 2 * (lane & 3);
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kp = kbase + n * 8 + (j & 1);
-        const int qp = qpos0 + (j >> 1) * 8;
-        const float v = kp <= qp ? s[n][j] * sl2 : -INFINITY;
-        s[n][j] = v;
-        if (j >> 1) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
-      }
+      mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float mn0 = fmaxf(m0, mx0 * sl2), mn1 = fmaxf(m1, mx1 * sl2);      // scale > 0 (checked by the launcher)
     const float e0 = mn0 == -INFINITY ? 0.f : mn0, e1 = mn1 == -INFINITY ? 0.f : mn1;
-    const float r0 = exp2f(m0 - e0), r1 = exp2f(m1 - e1);      // exp2(-inf) = 0 when nothing was seen yet
+    const float r0 = ex2_approx(m0 - e0), r1 = ex2_approx(m1 - e1);          // 2^(-inf) = 0 when nothing was seen yet
     m0 = mn0; m1 = mn1;
     l0 *= r0; l1 *= r1;
 #pragma unroll
@@ -500,22 +543,21 @@ paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, c
     uint32_t pa[4][4];                                  // P as A fragments: 4 k-steps of 16 keys
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
-      const float p0 = exp2f(s[n][0] - e0), p1 = exp2f(s[n][1] - e0), p2 = exp2f(s[n][2] - e1), p3 = exp2f(s[n][3] - e1);
-      // the sums use the probabilities as they are multiplied (rounded to bf16), so numerator and denominator agree
-      const uint32_t lo = pack_bf16x2(p0, p1), hi = pack_bf16x2(p2, p3);
-      const float2 flo = unpack_bf16x2(lo), fhi = unpack_bf16x2(hi);
-      l0 += flo.x + flo.y;
-      l1 += fhi.x + fhi.y;
-      pa[n >> 1][(n & 1) * 2] = lo;
-      pa[n >> 1][(n & 1) * 2 + 1] = hi;
+      const float p0 = ex2_approx(fmaf(s[n][0], sl2, -e0)), p1 = ex2_approx(fmaf(s[n][1], sl2, -e0));
+      const float p2 = ex2_approx(fmaf(s[n][2], sl2, -e1)), p3 = ex2_approx(fmaf(s[n][3], sl2, -e1));
+      l0 += p0 + p1;
+      l1 += p2 + p3;
+      pa[n >> 1][(n & 1) * 2] = pack_bf16x2(p0, p1);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(p2, p3);
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-      for (int n = 0; n < 2 * DK; ++n) {
-        uint32_t b0, b1;
-        ldsm_x2_trans(smem_u32(bv + (kk * 16 + (lane & 15)) * LD + n * 8), b0, b1);
+      for (int n = 0; n < 2 * DK; n += 2) {             // one ldmatrix.x4.trans feeds two output column tiles
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_trans(smem_u32(bv + (kk * 16 + (lane & 15)) * LD + n * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
         mma_bf16_16816(o[n], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+        mma_bf16_16816(o[n + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
       }
     }
     __syncthreads();                                    // everyone is done with `buf` before the next prefetch lands in it
@@ -524,7 +566,7 @@ paged_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, c
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  if (sinks) { l0 += exp2f(sink2 - m0); l1 += exp2f(sink2 - m1); }
+  if (sinks) { l0 += ex2_approx(sink2 - m0); l1 += ex2_approx(sink2 - m1); }
   const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
   const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
 #pragma unroll
@@ -542,11 +584,14 @@ static int launch_mma(const void* q, long long q_stride, const void* ck, const v
                       const int* table, int max_blocks, const float* sinks, void* out, int H, int G, int block_size, float scale,
                       cudaStream_t st) {
   constexpr int LD = 16 * DK + 8;
-  const size_t smem = (size_t)(kTQ + 4 * kTK) * LD * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(4 * kTK) * LD * sizeof(__nv_bfloat16);
   auto kern = paged_attn_mma_kernel<DK>;
   if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int bs_log2 = 0;
+  while ((1 << bs_log2) < block_size) ++bs_log2;
+  if ((1 << bs_log2) != block_size) return B200_ERR_UNSUPPORTED;
   kern<<<dim3(n_tiles, H), 128, smem, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)ck, (const __nv_bfloat16*)cv,
-                                             tiles, table, max_blocks, sinks, (__nv_bfloat16*)out, H, G, block_size, scale);
+                                             tiles, table, max_blocks, sinks, (__nv_bfloat16*)out, H, G, bs_log2, scale);
   B200_LAUNCH_CHECK();
   return 0;
 }
@@ -640,7 +685,7 @@ B200_API int b200_paged_attn_mma(const void* q, long long q_stride, const void* 
                                  int block_size, float scale, int dtype, void* stream_) {
   cudaStream_t st = (cudaStream_t)stream_;
   if (n_tiles <= 0) return 0;
-  if (dtype != B200_DT_BF16 || D % 16 || D < 16 || D > 128) return B200_ERR_UNSUPPORTED;
+  if (dtype != B200_DT_BF16 || D % 16 || D < 16 || D > 128 || !(scale > 0.f)) return B200_ERR_UNSUPPORTED;
   if (H <= 0 || G <= 0 || H % G || block_size <= 0 || (q_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15)) return B200_ERR_BAD_SHAPE;
 #define MMA(DK) case DK: return launch_mma<DK>(q, q_stride, ck, cv, (const int*)tiles, n_tiles, (const int*)table, max_blocks, \
                                                 (const float*)sinks, out, H, G, block_size, scale, st)

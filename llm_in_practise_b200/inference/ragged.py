@@ -33,9 +33,8 @@ class Pieces:
     n_tiles: int
     longest: int                    # tokens of the longest run
 
-    def use_mma(self, q: torch.Tensor, head_dim: int, window: int) -> bool:
-        import os
-        return (self.longest >= 8 and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
+    def use_mma(self, q: torch.Tensor, head_dim: int, window: int, scale: float = 1.0) -> bool:
+        return (self.longest >= 8 and scale > 0 and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and window == 0 and os.environ.get("B200_PAGED_MMA", "1") != "0")
 
 

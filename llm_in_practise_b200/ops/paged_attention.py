@@ -84,7 +84,7 @@ def paged_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tenso
     BS = cache_k.shape[2]
     if nv.use_native(q):
         out = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
-        if pieces is not None and pieces.use_mma(q, D, window):
+        if pieces is not None and pieces.use_mma(q, D, window, scale) and BS & (BS - 1) == 0:
             fn = nv.proto("b200_paged_attn_mma", [vp, i64, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, vp])
             nv.check(fn(nv.ptr(q), q.stride(0), nv.ptr(cache_k), nv.ptr(cache_v), nv.ptr(pieces.tiles), pieces.n_tiles,
                         nv.ptr(table), table.shape[1], nv.ptr(sinks), nv.ptr(out), H, G, D, BS, scale,
