@@ -444,6 +444,50 @@ int b200_gemv_fused(const b200_gemv_fused_args* a, void* stream);
  * LLM-Distributed-Training/04-DeepSpeed/ds_zero2_offload.json). */
 int b200_fold_grad(void* x, float* y, long long n, float scale, int clear_x, int dtype, void* stream);
 
+/* ---- ragged serving step over a paged KV cache (csrc/paged_attn.cu, norm.cu, elementwise.cu, moe.cu, gemm_simt.cu) ----
+ * A step is a flat list of tokens; token t sits at position pos[t] of the sequence in cache row slot[t] (int32 arrays).
+ * Caches are [blocks, Hkv, block_size, D] per layer, table is int32 [rows, max_blocks] (logical -> physical block).
+ * What vLLM's paged attention and fused layer ops do behind the reference's `vllm serve` deployments
+ * (LLM_on_Kubernetes/Inference_Platfrom/README.md:1504-1509). */
+
+/* Rotate the first `rot` dims of the H query and G key heads of qkv [tokens, row_stride] in place (pairs (2i, 2i+1) if
+ * interleaved, else (i, i + rot/2); cos / sin fp32 [max_pos, rot/2]) and store the keys at (slot, pos) of ck; the values
+ * stored in cv are the keys before rotation (v_from_k) or the G heads that follow the keys in the row. */
+int b200_rope_paged_store(void* qkv, long long row_stride, const void* cos_t, const void* sin_t, const void* pos, const void* slot,
+                          const void* table, int max_blocks, void* ck, void* cv, int tokens, int H, int G, int D, int rot,
+                          int block_size, int interleaved, int v_from_k, int dtype, void* stream);
+/* out [tokens, H * D]: token t over keys max(0, pos + 1 - window) .. pos of its row (window 0: all). sinks: fp32 [H] or NULL,
+ * a logit per head that only enters the softmax denominator. nsplit > 1 cuts every token's keys into ranges (part: fp32
+ * [tokens, H, nsplit, D + 2] scratch). fp32 arithmetic; D <= 256; 16-bit or fp32 cache. */
+int b200_paged_attn(const void* q, long long q_stride, const void* ck, const void* cv, const void* pos, const void* slot,
+                    const void* table, int max_blocks, const void* sinks, void* out, void* part, int tokens, int H, int G, int D,
+                    int block_size, float scale, int window, int nsplit, int dtype, void* stream);
+/* bf16 prompt pieces on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row, cache row).
+ * D % 16 == 0, D <= 128, block_size a power of two, scale > 0; else B200_ERR_UNSUPPORTED (use b200_paged_attn). */
+int b200_paged_attn_mma(const void* q, long long q_stride, const void* ck, const void* cv, const void* tiles, int n_tiles,
+                        const void* table, int max_blocks, const void* sinks, void* out, int H, int G, int D, int block_size,
+                        float scale, int dtype, void* stream);
+/* x = res_in + rms(y) * (off + w_post); h = rms(x) * (off + w_next). x -> res_out (fp32). y NULL: nothing is added; w_post
+ * NULL: y is added as it is; res_in NULL: zero; w_next NULL: no h. Statistics and the stream are fp32. */
+int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
+                       long long rows, int cols, float eps, float off, int y_dtype, int h_dtype, int w_dtype, void* stream);
+/* y [rows, F] = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit), u = clamp(up, +-limit) over gu [rows, 2F]
+ * (gate | up); limit <= 0: no clamps. */
+int b200_clamped_glu(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, int dtype, void* stream);
+/* x <- cap * tanh(x / cap) on n fp32 values. */
+int b200_softcap(float* x, long long n, float cap, void* stream);
+/* Router of a token-choice MoE in fp32: z = h W_r^T + bias, the `top` largest per token -> top_i (int64 [tokens, top]) and
+ * top_p (fp32): mode 0 softmax over the chosen logits, 1 chosen entries of the softmax over all, 2 those renormalised.
+ * logits_out: optional fp32 [tokens, E]. */
+int b200_moe_route(const void* h, const void* wr, const float* bias, long long* top_i, float* top_p, float* logits_out,
+                   long long tokens, int W, int E, int top, int mode, int h_dtype, int w_dtype, void* stream);
+/* out fp32 [tokens, W] = sum_k p[t, k] * y[dest[t * top + k]] (y: expert-sorted rows of a grouped GEMM). */
+int b200_moe_combine(const void* y, const long long* dest, const float* p, float* out, long long tokens, int W, int top, int dtype,
+                     void* stream);
+/* D [M, N] = A [M, K] B[N, K]^T in true fp32 (FFMA; no TF32 rounding of the operands); any sizes and row strides. */
+int b200_gemm_f32_exact(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

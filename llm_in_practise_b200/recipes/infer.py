@@ -24,7 +24,7 @@ import sys
 import torch
 
 from ..data.chat import deepseek_prompt
-from ..inference import GenerationConfig, Generator, chat, stream_generate
+from ..inference import GenerationConfig, Generator, chat, make_generator, stream_generate
 from ..io.hf import from_pretrained
 
 
@@ -84,7 +84,7 @@ def main(argv=None):
                     help="serve: GiB of pinned host memory for cached prefixes that lose their HBM row (LMCache-style tier)")
     ap.add_argument("--enforce-eager", dest="enforce_eager", action="store_true", help="serve: no CUDA-graph warm-up at start")
     ap.add_argument("--prompt_style", default="chatml", choices=["chatml", "deepseek"])
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
     ap.add_argument("--tensor-parallel-size", "--tensor_parallel_size", dest="tp", type=int, default=1,
                     help="serve: ranks that share every layer (vllm serve --tensor-parallel-size; launch under torchrun)")
     ap.add_argument("--pipeline-parallel-size", "--pipeline_parallel_size", dest="pp", type=int, default=1,
@@ -107,7 +107,7 @@ def main(argv=None):
             ap.error(f"--quantization {a.quantization}: {a.model} is not a quantised checkpoint (no quantization_config found)")
     dev = getattr(model, "base_model", model).embed_tokens.device
     eos = [t for t in (getattr(tok, "eos_token_id", None),) if t is not None]
-    gen = Generator(model, tok, a.max_model_len)
+    gen = make_generator(model, tok, a.max_model_len)      # by the model's kind (registry: models/__init__.py)
 
     if a.cmd == "once":
         ids = _ids(tok, deepseek_prompt(a.prompt), dev)
