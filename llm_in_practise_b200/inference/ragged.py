@@ -153,7 +153,7 @@ class RaggedGenerator(Generator):
     # ------------------------------------------------------------------ single-process generation
     def _generate(self, input_ids: torch.Tensor, config: Optional[GenerationConfig], streamer, seed: Optional[int],
                   return_logprobs: bool, **kw):
-        """Same contract as ``Generator.generate``: [B, S] prompts -> [B, S + new] ids. The prompts are one ragged step, every
+        """Same interface as ``Generator.generate``: [B, S] prompts -> [B, S + new] ids. The prompts are one ragged step, every
         following step decodes one token per unfinished sequence."""
         cfg = config or GenerationConfig(**{k: v for k, v in kw.items() if k in GenerationConfig.__dataclass_fields__})
         eos = cfg.eos_token_id

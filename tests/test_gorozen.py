@@ -186,7 +186,7 @@ def _pieces(device, runs):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("H,G,D,BS", [(4, 2, 32, 64), (3, 3, 24, 16), (8, 1, 48, 64), (2, 1, 128, 32)])
+@pytest.mark.parametrize("H,G,D,BS", [(4, 2, 32, 64), (3, 3, 24, 16), (6, 2, 48, 64), (2, 1, 128, 32)])
 def test_paged_attention_with_sinks(device, dtype, H, G, D, BS):
     from llm_in_practise_b200.ops.paged_attention import paged_attention
     g = torch.Generator().manual_seed(3)
