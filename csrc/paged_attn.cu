@@ -14,7 +14,7 @@
 //                           scalar one for head sizes that are not whole chunks. `nsplit` > 1 cuts the keys of every token
 //                           into that many ranges (long-context decode); a second kernel merges the partial
 //                           (max, sum, acc) triples.
-//   b200_paged_attn_mma     16-bit prompt pieces on the tensor cores (mma.sync m16n8k16): 64 query rows of one piece per
+//   b200_paged_attn_mma     bf16 prompt pieces on the tensor cores (mma.sync m16n8k16): 64 query rows of one piece per
 //                           CTA, one cache page (or 64 keys of it) per iteration.
 //
 // A sink is a per-head logit that takes part in the softmax denominator only: the running maximum starts at the sink and
