@@ -560,6 +560,34 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, 
   else y[idx] = ov[0];
 }
 
+// y = act(gate) * up; ACT 0: silu, 1: tanh-form GELU, 2: erf GELU
+template <typename T, int V, int ACT>
+__global__ void act_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F) {
+  const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
+  if (idx >= rows * F) return;
+  const long long r = idx / F;
+  const int c = (int)(idx - r * F);
+  T gv[V], uv[V], ov[V];
+  if (V > 1) {
+    *reinterpret_cast<uint4*>(gv) = *reinterpret_cast<const uint4*>(gu + r * 2 * F + c);
+    *reinterpret_cast<uint4*>(uv) = *reinterpret_cast<const uint4*>(gu + r * 2 * F + F + c);
+  } else {
+    gv[0] = gu[r * 2 * F + c];
+    uv[0] = gu[r * 2 * F + F + c];
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const float g = to_f32<T>(gv[j]), u = to_f32<T>(uv[j]);
+    float a;
+    if (ACT == 0) a = g / (1.f + expf(-g));
+    else if (ACT == 1) a = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
+    ov[j] = from_f32<T>(a * u);
+  }
+  if (V > 1) *reinterpret_cast<uint4*>(y + idx) = *reinterpret_cast<const uint4*>(ov);
+  else y[idx] = ov[0];
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
@@ -580,6 +608,25 @@ B200_API int b200_clamped_glu(const void* gu, void* y, long long rows, int F, fl
     const unsigned grid = (unsigned)((rows * F + tb - 1) / tb);
     B200_DISPATCH_T(dtype, clamped_glu_kernel<T, 1><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F, limit, alpha, shift));
   }
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_act_glu(const void* gu, void* y, long long rows, int F, int act, int dtype, void* stream) {
+  using namespace b200;
+  if (rows <= 0 || F <= 0) return rows == 0 ? 0 : B200_ERR_BAD_SHAPE;
+  if (act < 0 || act > 2) return B200_ERR_UNSUPPORTED;
+  const int tb = 256;
+  const int V = dtype == B200_DT_FP32 ? 4 : 8;
+  const bool vec = F % V == 0 && !((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15);
+  const unsigned grid = (unsigned)(((vec ? rows * F / V : rows * F) + tb - 1) / tb);
+#define GLU_ACT(ACT)                                                                                                       \
+  do {                                                                                                                     \
+    if (vec) { B200_DISPATCH_T(dtype, act_glu_kernel<T, 16 / sizeof(T), ACT><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F)); } \
+    else { B200_DISPATCH_T(dtype, act_glu_kernel<T, 1, ACT><<<grid, tb, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)y, rows, F)); } \
+  } while (0)
+  if (act == 0) GLU_ACT(0); else if (act == 1) GLU_ACT(1); else GLU_ACT(2);
+#undef GLU_ACT
   B200_LAUNCH_CHECK();
   return 0;
 }

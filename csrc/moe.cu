@@ -4,8 +4,13 @@
 //                      experts per token and their weights. mode 0: softmax over the chosen logits only; mode 1: softmax
 //                      over all experts, chosen probabilities kept as they are; mode 2: mode 1 renormalised to sum 1.
 //                      One warp per token; ties go to the lower expert index.
-//   b200_moe_combine   out[t] = sum_k p[t, k] * y[dest[t * top + k]] in fp32 (y: the expert-sorted rows the grouped GEMM
-//                      wrote), a fixed order of additions per token.
+//   b200_moe_route_grouped   sigmoid router with group-limited choice: s = sigmoid(W_r h); the choice is made on
+//                      s + correction, only among the experts of the `keep` groups (of `groups` equal runs of neighbours)
+//                      whose `group_top` largest choice scores sum highest; the weights are s of the chosen experts, as
+//                      they are or renormalised to sum 1. Rows of W_r past the experts are per-token gates: their sigmoid
+//                      goes to gate_out (the gate of a shared expert). One warp per token; ties go to the lower index.
+//   b200_moe_combine   out[t] = sum_k p[t, k] * y[dest[t * top + k]] (+ gate[t] * shared[t]) in fp32 (y: the expert-sorted
+//                      rows the grouped GEMM wrote), a fixed order of additions per token.
 #include "common.cuh"
 #include "../include/b200_ops.h"
 
@@ -56,15 +61,87 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const floa
     for (int k = 0; k < top; ++k) top_p[t * top + k] /= psum;
 }
 
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(128)
+moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const float* __restrict__ corr,
+                         long long* __restrict__ top_i, float* __restrict__ top_p, float* __restrict__ gate_out, long long tokens,
+                         int W, int E, int X, int top, int groups, int keep, int group_top, int renorm) {
+  extern __shared__ float zbuf[];                     // per warp: s [E + X], choice [E], group score [groups]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= tokens) return;
+  float* s = zbuf + warp * (2 * E + X + groups);
+  float* choice = s + E + X;
+  float* gs = choice + E;
+  const TH* hr = h + t * W;
+  for (int e = 0; e < E + X; ++e) {
+    const TW* w = wr + (long long)e * W;
+    float a = 0.f;
+    for (int i = lane; i < W; i += 32) a = fmaf(to_f32<TH>(hr[i]), to_f32<TW>(w[i]), a);
+    a = warp_sum(a);
+    if (lane == 0) s[e] = 1.f / (1.f + expf(-a));
+  }
+  __syncwarp();
+  if (lane != 0) return;
+  for (int x = 0; x < X; ++x) gate_out[t * X + x] = s[E + x];
+  for (int e = 0; e < E; ++e) choice[e] = s[e] + (corr ? corr[e] : 0.f);
+  const int per = E / groups;
+  if (keep < groups) {
+    for (int g = 0; g < groups; ++g) {                 // sum of the group's `group_top` largest choice scores
+      float sum = 0.f;
+      int last = -1;
+      float lastv = INFINITY;
+      for (int k = 0; k < group_top && k < per; ++k) {   // k-th largest in (value desc, index asc) order
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = choice[e];
+          const bool after = v < lastv || (v == lastv && e > last);
+          if (after && (best < 0 || v > bv)) { best = e; bv = v; }
+        }
+        if (best < 0) break;
+        sum += bv;
+        last = best;
+        lastv = bv;
+      }
+      gs[g] = sum;
+    }
+    for (int k = 0; k < keep; ++k) {                   // mark the kept groups with NaN-free flags: +inf = kept
+      int best = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < groups; ++g)
+        if (gs[g] != INFINITY && (best < 0 || gs[g] > bv)) { best = g; bv = gs[g]; }
+      gs[best] = INFINITY;
+    }
+    for (int e = 0; e < E; ++e)
+      if (gs[e / per] != INFINITY) choice[e] = -INFINITY;
+  }
+  float psum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    int best = 0;
+    float bv = choice[0];
+    for (int e = 1; e < E; ++e)
+      if (choice[e] > bv) { best = e; bv = choice[e]; }
+    choice[best] = -INFINITY;                          // taken
+    top_i[t * top + k] = best;
+    top_p[t * top + k] = s[best];
+    psum += s[best];
+  }
+  if (renorm)
+    for (int k = 0; k < top; ++k) top_p[t * top + k] /= psum;
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const long long* __restrict__ dest, const float* __restrict__ p,
-                                   float* __restrict__ out, long long tokens, int W, int top) {
+                                   const T* __restrict__ shared, const float* __restrict__ gate, float* __restrict__ out,
+                                   long long tokens, int W, int top) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= tokens * W) return;
   const long long t = idx / W;
   const int c = (int)(idx - t * W);
   float a = 0.f;
   for (int k = 0; k < top; ++k) a = fmaf(p[t * top + k], to_f32<T>(y[dest[t * top + k] * W + c]), a);
+  if (shared) a = fmaf(gate ? gate[t] : 1.f, to_f32<T>(shared[idx]), a);
   out[idx] = a;
 }
 
@@ -94,14 +171,42 @@ B200_API int b200_moe_route(const void* h, const void* wr, const float* bias, lo
   return 0;
 }
 
-B200_API int b200_moe_combine(const void* y, const long long* dest, const float* p, float* out, long long tokens, int W, int top,
-                              int dtype, void* stream) {
+B200_API int b200_moe_route_grouped(const void* h, const void* wr, const float* corr, long long* top_i, float* top_p,
+                                    float* gate_out, long long tokens, int W, int E, int X, int top, int groups, int keep,
+                                    int group_top, int renorm, int h_dtype, int w_dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens <= 0) return 0;
+  if (W <= 0 || E <= 0 || X < 0 || top <= 0 || top > E || E > 2048 || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+      group_top <= 0 || top > keep * (E / groups) || (X > 0 && !gate_out))
+    return B200_ERR_BAD_SHAPE;
+  const int warps = 4;
+  const unsigned grid = (unsigned)((tokens + warps - 1) / warps);
+  const size_t smem = (size_t)warps * (2 * E + X + groups) * sizeof(float);
+  typedef __nv_bfloat16 bf;
+#define RG(TH, TW)                                                                                                          \
+  moe_route_grouped_kernel<TH, TW><<<grid, warps * 32, smem, st>>>((const TH*)h, (const TW*)wr, corr, top_i, top_p, gate_out,    \
+                                                                  tokens, W, E, X, top, groups, keep, group_top, renorm)
+  if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_BF16) RG(bf, bf);
+  else if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_FP32) RG(bf, float);
+  else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_FP32) RG(float, float);
+  else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_BF16) RG(float, bf);
+  else return B200_ERR_UNSUPPORTED;
+#undef RG
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_moe_combine(const void* y, const long long* dest, const float* p, const void* shared, const float* gate,
+                              float* out, long long tokens, int W, int top, int dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens <= 0) return 0;
   const unsigned grid = (unsigned)((tokens * W + 255) / 256);
-  if (dtype == B200_DT_BF16) moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, dest, p, out, tokens, W, top);
-  else if (dtype == B200_DT_FP16) moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)y, dest, p, out, tokens, W, top);
-  else if (dtype == B200_DT_FP32) moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)y, dest, p, out, tokens, W, top);
+  if (dtype == B200_DT_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, dest, p, (const __nv_bfloat16*)shared, gate, out, tokens, W, top);
+  else if (dtype == B200_DT_FP16)
+    moe_combine_kernel<__half><<<grid, 256, 0, st>>>((const __half*)y, dest, p, (const __half*)shared, gate, out, tokens, W, top);
+  else if (dtype == B200_DT_FP32)
+    moe_combine_kernel<float><<<grid, 256, 0, st>>>((const float*)y, dest, p, (const float*)shared, gate, out, tokens, W, top);
   else return B200_ERR_UNSUPPORTED;
   B200_LAUNCH_CHECK();
   return 0;

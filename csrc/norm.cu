@@ -429,7 +429,7 @@ template <typename TY, typename TH, typename WT>
 __global__ void __launch_bounds__(kNormThreads)
 sandwich_norm_kernel(const TY* __restrict__ y, const WT* __restrict__ w_post, const float* __restrict__ res_in,
                      float* __restrict__ res_out, const WT* __restrict__ w_next, TH* __restrict__ h, int cols, float eps,
-                     float off) {
+                     float off, float mult) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   const long long row = blockIdx.x;
@@ -454,12 +454,17 @@ sandwich_norm_kernel(const TY* __restrict__ y, const WT* __restrict__ w_post, co
   for (int i = threadIdx.x; i < cols; i += blockDim.x) {
     float v = rowbuf[i];
     if (w_post) v = v * r1 * (off + to_f32<WT>(w_post[i]));
+    v *= mult;
     if (res_in) v += res_in[row * cols + i];
     rowbuf[i] = v;
     if (res_out) res_out[row * cols + i] = v;
     s2 += v * v;
   }
-  if (!w_next) return;
+  if (!w_next) {                                        // no norm follows: h, if asked for, is the stream in the next GEMM's dtype
+    if (h)
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) h[row * cols + i] = from_f32<TH>(rowbuf[i]);
+    return;
+  }
   s2 = block_sum(s2, red);
   const float r2 = 1.f / sqrtf(s2 / (float)cols + eps);
   for (int i = threadIdx.x; i < cols; i += blockDim.x)
@@ -468,7 +473,7 @@ sandwich_norm_kernel(const TY* __restrict__ y, const WT* __restrict__ w_post, co
 
 template <typename TY, typename TH, typename WT>
 static int sandwich_launch(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
-                           long long rows, int cols, float eps, float off, cudaStream_t st) {
+                           long long rows, int cols, float eps, float off, float mult, cudaStream_t st) {
   const size_t smem = (size_t)cols * sizeof(float);
   auto kern = sandwich_norm_kernel<TY, TH, WT>;
   if (smem > 48 * 1024) {
@@ -476,21 +481,21 @@ static int sandwich_launch(const void* y, const void* w_post, const float* res_i
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   kern<<<(unsigned)rows, kNormThreads, smem, st>>>((const TY*)y, (const WT*)w_post, res_in, res_out, (const WT*)w_next, (TH*)h,
-                                                   cols, eps, off);
+                                                   cols, eps, off, mult);
   B200_LAUNCH_CHECK();
   return 0;
 }
 }  // namespace b200
 
 B200_API int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next,
-                                void* h, long long rows, int cols, float eps, float off, int y_dtype, int h_dtype, int w_dtype,
-                                void* stream) {
+                                void* h, long long rows, int cols, float eps, float off, float mult, int y_dtype, int h_dtype,
+                                int w_dtype, void* stream) {
   using namespace b200;
   cudaStream_t st = (cudaStream_t)stream;
   if (rows <= 0) return 0;
   if (cols <= 0) return B200_ERR_BAD_SHAPE;
   typedef __nv_bfloat16 bf;
-#define SW(TY, TH, WT) return sandwich_launch<TY, TH, WT>(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, st)
+#define SW(TY, TH, WT) return sandwich_launch<TY, TH, WT>(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, mult, st)
   if (w_dtype == B200_DT_BF16) {
     if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_BF16) SW(float, bf, bf);
     if (y_dtype == B200_DT_BF16 && h_dtype == B200_DT_BF16) SW(bf, bf, bf);

@@ -467,10 +467,12 @@ int b200_paged_attn(const void* q, long long q_stride, const void* ck, const voi
 int b200_paged_attn_mma(const void* q, long long q_stride, const void* ck, const void* cv, const void* tiles, int n_tiles,
                         const void* table, int max_blocks, const void* sinks, void* out, int H, int G, int D, int block_size,
                         float scale, int dtype, void* stream);
-/* x = res_in + rms(y) * (off + w_post); h = rms(x) * (off + w_next). x -> res_out (fp32). y NULL: nothing is added; w_post
- * NULL: y is added as it is; res_in NULL: zero; w_next NULL: no h. Statistics and the stream are fp32. */
+/* x = res_in + mult * rms(y) * (off + w_post); h = rms(x) * (off + w_next). x -> res_out (fp32). y NULL: nothing is added;
+ * w_post NULL: mult * y is added as it is; res_in NULL: zero; w_next NULL: h (if not NULL) = x in h_dtype. Statistics and
+ * the stream are fp32. */
 int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
-                       long long rows, int cols, float eps, float off, int y_dtype, int h_dtype, int w_dtype, void* stream);
+                       long long rows, int cols, float eps, float off, float mult, int y_dtype, int h_dtype, int w_dtype,
+                       void* stream);
 /* y [rows, F] = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit), u = clamp(up, +-limit) over gu [rows, 2F]
  * (gate | up); limit <= 0: no clamps. */
 int b200_clamped_glu(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, int dtype, void* stream);
@@ -481,9 +483,45 @@ int b200_softcap(float* x, long long n, float cap, void* stream);
  * logits_out: optional fp32 [tokens, E]. */
 int b200_moe_route(const void* h, const void* wr, const float* bias, long long* top_i, float* top_p, float* logits_out,
                    long long tokens, int W, int E, int top, int mode, int h_dtype, int w_dtype, void* stream);
-/* out fp32 [tokens, W] = sum_k p[t, k] * y[dest[t * top + k]] (y: expert-sorted rows of a grouped GEMM). */
-int b200_moe_combine(const void* y, const long long* dest, const float* p, float* out, long long tokens, int W, int top, int dtype,
+/* Sigmoid router with group-limited choice, fp32: s = sigmoid(h W_r^T); choice = s + corr (corr fp32 [E] or NULL); only
+ * experts of the `keep` groups (of `groups` equal runs of neighbouring experts) whose `group_top` largest choice scores
+ * sum highest can be chosen; top_p = s of the chosen (renorm: divided by their sum). W_r has E + X rows: the sigmoid of
+ * the last X goes to gate_out fp32 [tokens, X] (per-token gates, e.g. of a shared expert). */
+int b200_moe_route_grouped(const void* h, const void* wr, const float* corr, long long* top_i, float* top_p, float* gate_out,
+                           long long tokens, int W, int E, int X, int top, int groups, int keep, int group_top, int renorm,
+                           int h_dtype, int w_dtype, void* stream);
+/* out fp32 [tokens, W] = sum_k p[t, k] * y[dest[t * top + k]] (y: expert-sorted rows of a grouped GEMM), plus
+ * gate[t] * shared[t] when shared ([tokens, W], y's dtype) is given (gate fp32 [tokens] or NULL = 1). */
+int b200_moe_combine(const void* y, const long long* dest, const float* p, const void* shared, const float* gate, float* out,
+                     long long tokens, int W, int top, int dtype, void* stream);
+/* y [rows, F] = act(gate) * up over gu [rows, 2F] (gate | up); act 0: silu, 1: tanh-form GELU, 2: erf GELU. */
+int b200_act_glu(const void* gu, void* y, long long rows, int F, int act, int dtype, void* stream);
+
+/* ---- attention over a cache of latent rows (csrc/latent_attn.cu) ----
+ * A layer caches one row [c | r] of Dk = C + R values per token (latent and shared rotated key part); cache is
+ * [blocks, block_size, Dk]. Queries arrive in the latent space, [tokens, H, Dk]; values are the first Dv columns of the
+ * cached rows. */
+/* proj fp32 [tokens, ld]: query latent at q_off (Cq columns, may be 0) -> RMS norm * wq -> cq_out [tokens, Cq]; KV latent at
+ * kv_off (C columns) -> RMS norm * wkv, then R columns whose first `rot` turn by the token's position (interleaved pairs;
+ * cos / sin fp32 [max_pos, rot / 2]) -> the token's cache row. */
+int b200_latent_kv_store(const float* proj, long long ld, int q_off, int Cq, int kv_off, int C, int R, int rot, const void* wq,
+                         const void* wkv, float eps, const float* cos_t, const float* sin_t, const int* pos, const int* slot,
+                         const int* table, int max_blocks, int block_size, void* cq_out, void* cache, int tokens, int dtype,
+                         int w_dtype, void* stream);
+/* The last R columns of every head of q [tokens, q_stride] (heads of D + R), turned like the keys -> qx[t, h, C .. C + R). */
+int b200_latent_q_rope(const void* q, long long q_stride, const float* cos_t, const float* sin_t, const int* pos, void* qx,
+                       int tokens, int H, int D, int R, int rot, int C, int dtype, void* stream);
+/* out [tokens, H, Dv]: causal attention of q [tokens, H, Dk] over rows 0 .. pos[t] of cache row slot[t]; fp32 arithmetic,
+ * Dk <= 1024, Dv <= min(Dk, 512); sinks fp32 [H] or NULL. */
+int b200_latent_attn(const void* q, const void* cache, const int* pos, const int* slot, const int* table, int max_blocks,
+                     const float* sinks, void* out, int tokens, int H, int Dk, int Dv, int block_size, float scale, int dtype,
                      void* stream);
+/* The same on mma.sync (bf16; Dk % 16 == 0, Dv even and <= 256, block_size a power of two, scale > 0; else
+ * B200_ERR_UNSUPPORTED). tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row, cache row), or NULL:
+ * n_tiles single tokens at (pos, slot), whose keys may be cut into nsplit ranges (part: fp32 [tokens, H, nsplit, Dv + 2]). */
+int b200_latent_attn_mma(const void* q, const void* cache, const int* tiles, int n_tiles, const int* pos, const int* slot,
+                         const int* table, int max_blocks, const float* sinks, void* out, float* part, int H, int Dk, int Dv,
+                         int block_size, float scale, int nsplit, int dtype, void* stream);
 /* D [M, N] = A [M, K] B[N, K]^T in true fp32 (FFMA; no TF32 rounding of the operands); any sizes and row strides. */
 int b200_gemm_f32_exact(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
                         void* stream);

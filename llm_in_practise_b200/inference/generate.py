@@ -99,14 +99,17 @@ class PagedKVCache(KVCache):
     (serve/engine.py); this class only holds the storage and the table."""
     paged = True
 
-    def __init__(self, n_layers, num_blocks, Hkv, block_size, D, dtype, device, max_seqs, max_len):
+    def __init__(self, n_layers, num_blocks, Hkv, block_size, D, dtype, device, max_seqs, max_len, Dv=None):
         if block_size & (block_size - 1):
             raise ValueError("block_size must be a power of two")
-        # Hkv / D may be lists: models whose layers differ in their KV heads or head size get one pool per layer
+        # Hkv / D may be lists: models whose layers differ in their KV heads or head size get one pool per layer. Dv: the value
+        # pool's row size per layer where it differs from the keys'; 0 = no value pool (layers whose values are a part of
+        # their key rows, e.g. a latent cache)
         hk = list(Hkv) if isinstance(Hkv, (list, tuple)) else [Hkv] * n_layers
         hd = list(D) if isinstance(D, (list, tuple)) else [D] * n_layers
+        hv = hd if Dv is None else (list(Dv) if isinstance(Dv, (list, tuple)) else [Dv] * n_layers)
         self.k = [torch.zeros(num_blocks, hk[i], block_size, hd[i], dtype=dtype, device=device) for i in range(n_layers)]
-        self.v = [torch.zeros(num_blocks, hk[i], block_size, hd[i], dtype=dtype, device=device) for i in range(n_layers)]
+        self.v = [torch.zeros(num_blocks, hk[i], block_size, hv[i], dtype=dtype, device=device) for i in range(n_layers)]
         self.block_size, self.num_blocks = block_size, num_blocks
         self.max_len = max_len
         self.max_blocks = -(-max_len // block_size)
@@ -132,7 +135,7 @@ class PagedKVCache(KVCache):
         blks = self.table[slot, :nb].long()
         Hkv, D = self.k[li].shape[1], self.k[li].shape[3]
         k = self.k[li].index_select(0, blks).permute(1, 0, 2, 3).reshape(Hkv, nb * self.block_size, D)
-        v = self.v[li].index_select(0, blks).permute(1, 0, 2, 3).reshape(Hkv, nb * self.block_size, D)
+        v = self.v[li].index_select(0, blks).permute(1, 0, 2, 3).reshape(Hkv, nb * self.block_size, self.v[li].shape[3])
         return k, v
 
 

@@ -53,15 +53,20 @@ class RaggedGenerator(Generator):
         """A paged cache with one pool per layer, each sized from that layer's own (kv heads, head size). Physical block 0
         is left to unset table entries; callers hand out blocks 1 .. num_blocks."""
         m = self.model
-        lay = m.kv_layout()
-        cache = PagedKVCache(len(lay), num_blocks + 1, [g for g, _ in lay], block_size, [d for _, d in lay], m.embed_tokens.dtype,
-                             m.embed_tokens.device, max_seqs + 1, max_len)
+        lay = self._kv_layout()
+        cache = PagedKVCache(len(lay), num_blocks + 1, [g for g, _, _ in lay], block_size, [d for _, d, _ in lay], m.embed_tokens.dtype,
+                             m.embed_tokens.device, max_seqs + 1, max_len, Dv=[dv for _, _, dv in lay])
         cache.scratch_row = max_seqs             # a row that never gets blocks: padding tokens of a bucketed batch write to block 0
         return cache
 
+    def _kv_layout(self):
+        """(kv heads, key row size, value row size) per layer; a model's ``kv_layout`` may give pairs (values sized like keys)
+        or triples (value size 0: the layer keeps no value pool, e.g. a latent cache whose rows serve as both)."""
+        return [(e[0], e[1], e[2] if len(e) > 2 else e[1]) for e in self.model.kv_layout()]
+
     def kv_token_bytes(self) -> int:
         es = self.model.embed_tokens.element_size()
-        return sum(2 * g * d * es for g, d in self.model.kv_layout())
+        return sum(g * (d + dv) * es for g, d, dv in self._kv_layout())
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()

@@ -11,11 +11,18 @@ def _load_gorozen(path, dtype, device):
     return gorozen_from_pretrained(path, dtype=dtype, device=device)
 
 
+def _load_segorax(path, dtype, device):
+    from .segorax import segorax_from_pretrained
+    return segorax_from_pretrained(path, dtype=dtype, device=device)
+
+
 # ``architecture`` (or HF ``model_type`` / ``architectures[0]``) of config.json -> loader(path, dtype, device).
 # Anything not listed is read as a Qwen2/Qwen3-style HF checkpoint by ``io.hf.from_pretrained``.
 MODEL_REGISTRY: Dict[str, Callable] = {
     "Gorozen": _load_gorozen,
     "gorozen": _load_gorozen,
+    "Segorax": _load_segorax,
+    "segorax": _load_segorax,
 }
 
 

@@ -60,9 +60,8 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, m
         if scaling.get("truncate", True):
             low, high = math.floor(low), math.ceil(high)
         low, high = max(low, 0), min(high, head_dim - 1)
-        if low == high:
-            high += 0.001
-        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0, 1)
+        span = max(high - low, 0.001)
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - low) / span).clamp(0, 1)
         keep = 1.0 - ramp                                       # 1: high-frequency dims keep their frequency, 0: interpolated
         return (inv / factor) * (1 - keep) + inv * keep, float(att)
     if kind == "llama3":
@@ -359,6 +358,26 @@ def clamped_glu(gate_up: torch.Tensor, limit: float = 0.0, alpha: float = 1.0, s
     if limit > 0:
         g, u = g.clamp(max=limit), u.clamp(-limit, limit)
     return (g * torch.sigmoid(alpha * g) * (u + shift)).to(gate_up.dtype)
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}
+
+
+def act_glu(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` over ``gate_up = [rows, 2F]`` (gate first) for any F; ``act``: ``silu``, ``gelu_tanh`` (the tanh
+    form, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or ``gelu`` (erf). fp32 arithmetic. Inference only."""
+    rows, F2 = gate_up.shape
+    Fh = F2 // 2
+    if nv.use_native(gate_up):
+        gu = gate_up.contiguous()
+        y = torch.empty(rows, Fh, dtype=gu.dtype, device=gu.device)
+        fn = nv.proto("b200_act_glu", [vp, vp, i64, i32, i32, i32, vp])
+        nv.check(fn(nv.ptr(gu), nv.ptr(y), rows, Fh, GLU_ACTS[act], nv.dtype_code(gu.dtype), nv.stream()), "act_glu")
+        nv.count_launch()
+        return y
+    g, u = gate_up[:, :Fh].float(), gate_up[:, Fh:].float()
+    a = F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh" if act == "gelu_tanh" else "none")
+    return (a * u).to(gate_up.dtype)
 
 
 def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:

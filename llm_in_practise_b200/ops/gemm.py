@@ -362,3 +362,32 @@ def linear_exact(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dty
     nv.check(fn(nv.ptr(xf), nv.ptr(wf), nv.ptr(y), M, N, K, xf.stride(0), wf.stride(0), y.stride(0), nv.stream()), "gemm_f32_exact")
     nv.count_launch()
     return y if out_dtype == torch.float32 else y.to(out_dtype)
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, w_kn: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One small projection per head, at the precision of the operands: ``x`` [T, H, K] (any strides with a contiguous last
+    dim, e.g. a slice of every head of a fused projection), ``w`` [H, N, K] (or [H, K, N] with ``w_kn``) -> [T, H, N],
+    ``out[t, h] = W_h x[t, h]`` (with ``w_kn`` the stored [K, N] matrix is applied transposed, ``W_h^T x[t, h]``). ``out`` may
+    be a strided [T, H, N] view (e.g. the leading columns of wider rows). 16-bit operands whose head slices TMA can address
+    (16-byte aligned starts and row strides) are one batched tcgen05 GEMM launch; everything else, and fp32, is a batched
+    fp32 product (no TF32), rounded once to the output dtype."""
+    T, H, K = x.shape
+    N = w.shape[2] if w_kn else w.shape[1]
+    if out is None:
+        out = torch.empty(T, H, N, dtype=x.dtype, device=x.device)
+    if T == 0:
+        return out
+    xa, oa = x.transpose(0, 1), out.transpose(0, 1)                     # [H, T, K], [H, T, N] views
+    es = x.element_size()
+    ok = (nv.use_native(x) and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and out.dtype == x.dtype
+          and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous() and K % 8 == 0 and N % 8 == 0
+          and all(t.data_ptr() % 16 == 0 for t in (x, w, out))
+          and all((st * es) % 16 == 0 for st in (x.stride(0), x.stride(1), out.stride(0), out.stride(1))))
+    if ok:
+        gemm(xa, w, b_mn=w_kn, out=oa)
+        return out
+    wf = w.float()
+    y = torch.bmm(xa.float(), wf if w_kn else wf.transpose(1, 2))       # [H, T, N] fp32
+    oa.copy_(y)
+    return out
+

@@ -199,29 +199,80 @@ def route_topk(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Ten
     return ti, (tv / tv.sum(-1, keepdim=True) if mode == ROUTE_SOFTMAX_ALL_RENORM else tv)
 
 
-def moe_combine(y: torch.Tensor, dest: torch.Tensor, top_p: torch.Tensor) -> torch.Tensor:
-    """fp32 [T, D]: ``sum_k top_p[t, k] * y[dest[t * top + k]]`` over the expert-sorted rows ``y`` of a grouped GEMM."""
+def route_sigmoid_grouped(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int = 1,
+                          keep: int = 1, group_top: int = 2, renorm: bool = False, gate_rows: int = 0):
+    """Sigmoid router with a group-limited choice, in fp32 (``b200_moe_route_grouped``). Scores ``s = sigmoid(h W_r^T)``; the
+    choice is made on ``s + correction`` (a per-expert offset that steers the load without entering the weights), and only
+    among the experts of the ``keep`` groups — ``groups`` equal runs of neighbouring experts — whose ``group_top`` largest
+    choice scores sum highest (the other groups' choice scores count as minus infinity). Returns the chosen experts (long
+    [T, top]), their weights ``s`` (fp32 [T, top]; divided by their sum with ``renorm``) and, when ``w_router`` carries
+    ``gate_rows`` more rows after the experts', the sigmoid of those rows' logits (fp32 [T, gate_rows]; else None) — the
+    per-token gate of a shared expert comes out of the same pass over ``h``. Ties go to the lower index."""
+    T, W = h.shape
+    E = w_router.shape[0] - gate_rows
+    if nv.use_native(h):
+        h = h.contiguous()
+        top_i = torch.empty(T, top, dtype=torch.long, device=h.device)
+        top_p = torch.empty(T, top, dtype=torch.float32, device=h.device)
+        gate = torch.empty(T, gate_rows, dtype=torch.float32, device=h.device) if gate_rows else None
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        fn = nv.proto("b200_moe_route_grouped", [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp])
+        nv.check(fn(nv.ptr(h), nv.ptr(w_router), nv.ptr(correction), nv.ptr(top_i), nv.ptr(top_p), nv.ptr(gate), T, W, E, gate_rows, top,
+                    groups, keep, group_top, int(renorm), nv.dtype_code(h.dtype), nv.dtype_code(w_router.dtype), nv.stream()),
+                 "moe_route_grouped")
+        nv.count_launch()
+        return top_i, top_p, gate
+    s_all = torch.sigmoid(h.float() @ w_router.float().t())
+    s, gate = s_all[:, :E], (s_all[:, E:].contiguous() if gate_rows else None)
+    choice = s + correction.float() if correction is not None else s.clone()
+    if keep < groups:
+        per = E // groups
+        gs = choice.view(T, groups, per).topk(min(group_top, per), -1).values.sum(-1)
+        order = torch.argsort(gs, dim=-1, descending=True, stable=True)[:, :keep]
+        kept = torch.zeros(T, groups, dtype=torch.bool, device=h.device).scatter_(1, order, True)
+        choice = choice.masked_fill(~kept.repeat_interleave(per, 1), float("-inf"))
+    top_i = torch.argsort(choice, dim=-1, descending=True, stable=True)[:, :top]
+    top_p = s.gather(1, top_i)
+    if renorm:
+        top_p = top_p / top_p.sum(-1, keepdim=True)
+    return top_i, top_p, gate
+
+
+def moe_combine(y: torch.Tensor, dest: torch.Tensor, top_p: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 [T, D]: ``sum_k top_p[t, k] * y[dest[t * top + k]]`` over the expert-sorted rows ``y`` of a grouped GEMM, plus
+    ``gate[t] * shared[t]`` when a shared expert's output ``shared`` [T, D] (y's dtype) is given (``gate`` fp32 [T] or [T, 1];
+    None = 1)."""
     T, top = top_p.shape
     W = y.shape[1]
     if nv.use_native(y):
         out = torch.empty(T, W, dtype=torch.float32, device=y.device)
+        if shared is not None:
+            shared = shared.contiguous()
+            if shared.dtype != y.dtype:
+                raise TypeError("the shared expert's rows must have the routed rows' dtype")
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        fn = nv.proto("b200_moe_combine", [vp, vp, vp, vp, i64, i32, i32, i32, vp])
-        nv.check(fn(nv.ptr(y), nv.ptr(dest), nv.ptr(top_p), nv.ptr(out), T, W, top, nv.dtype_code(y.dtype), nv.stream()), "moe_combine")
+        fn = nv.proto("b200_moe_combine", [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp])
+        nv.check(fn(nv.ptr(y), nv.ptr(dest), nv.ptr(top_p), nv.ptr(shared), nv.ptr(gate), nv.ptr(out), T, W, top, nv.dtype_code(y.dtype),
+                    nv.stream()), "moe_combine")
         nv.count_launch()
         return out
-    return (y.index_select(0, dest).float().view(T, top, W) * top_p.unsqueeze(-1)).sum(1)
+    out = (y.index_select(0, dest).float().view(T, top, W) * top_p.unsqueeze(-1)).sum(1)
+    if shared is not None:
+        out = out + (shared.float() * gate.float().view(T, 1) if gate is not None else shared.float())
+    return out
 
 
 def gated_moe_ffn(h: torch.Tensor, top_i: torch.Tensor, top_p: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                  act, tile: int = TILE) -> torch.Tensor:
-    """Token-choice MoE of gated experts for inference: ``sum_k p_k * W_down[e_k] act(W_gate_up[e_k] h)`` -> fp32 [T, D].
-    ``w_gate_up`` [E, 2F, D] (gate rows first), ``w_down`` [E, D, F], ``act`` maps [rows, 2F] -> [rows, F]. Tokens are
-    counting-sorted by expert on the device (``dispatch``), both projections are one grouped GEMM each, and the weighted
-    sum over a token's experts is taken in fp32 in a fixed order (``moe_combine``)."""
+                  act, tile: int = TILE, shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token-choice MoE for inference: ``sum_k p_k * W_down[e_k] act(W_in[e_k] h)`` -> fp32 [T, D]. Gated experts:
+    ``w_gate_up`` [E, 2F, D] (gate rows first) and ``act`` maps [rows, 2F] -> [rows, F]; plain experts: ``w_gate_up`` is the
+    up projection [E, F, D] and ``act`` an elementwise activation. ``w_down`` [E, D, F]. Tokens are counting-sorted by expert
+    on the device (``dispatch``), both projections are one grouped GEMM each, and the weighted sum over a token's experts
+    (plus ``gate * shared``, a shared expert's rows, when given) is taken in fp32 in a fixed order (``moe_combine``)."""
     E = w_gate_up.shape[0]
     d = dispatch(top_i, E, tile)
     xs = torch.zeros(d.rows, h.shape[1], dtype=h.dtype, device=h.device).index_copy(0, d.dest, h.index_select(0, d.tok))
     mid = act(grouped_linear(xs, w_gate_up, None, d, tile))
     y = grouped_linear(mid, w_down, None, d, tile)
-    return moe_combine(y.contiguous(), d.dest, top_p)
+    return moe_combine(y.contiguous(), d.dest, top_p, shared, gate)

@@ -154,11 +154,13 @@ class LayerNorm(torch.nn.Module):
 
 def sandwich_norm(y: Optional[torch.Tensor], post_w: Optional[torch.Tensor], residual: Optional[torch.Tensor],
                   next_w: Optional[torch.Tensor], eps: float, weight_offset: float = 1.0,
-                  out_dtype: Optional[torch.dtype] = None) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+                  out_dtype: Optional[torch.dtype] = None, branch_mult: float = 1.0,
+                  cast_next: bool = False) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
     """Post-sublayer norm, residual add and the next pre-sublayer norm in one pass over a 32-bit residual stream
-    (``b200_sandwich_norm``): ``x = residual + rms(y) * (offset + post_w)``; ``h = rms(x) * (offset + next_w)``.
-    ``post_w`` None: ``y`` is added as it is (the embedding entering the stream); ``residual`` None: the stream starts at
-    zero; ``next_w`` None: no ``h`` (nothing follows). Gains are stored as a difference from ``weight_offset`` (1 for
+    (``b200_sandwich_norm``): ``x = residual + branch_mult * rms(y) * (offset + post_w)``; ``h = rms(x) * (offset + next_w)``.
+    ``post_w`` None: ``branch_mult * y`` is added as it is (the embedding entering the stream); ``residual`` None: the stream
+    starts at zero; ``next_w`` None: no ``h`` (nothing follows), or with ``cast_next`` ``h`` is ``x`` itself in ``out_dtype``
+    (designs whose sublayers read the stream un-normed). Gains are stored as a difference from ``weight_offset`` (1 for
     zero-centred gains, 0 for plain ones). Returns ``(h, x)`` with ``x`` fp32 and ``h`` in ``out_dtype`` (default: y's)."""
     src = y if y is not None else residual
     rows, cols = src.shape
@@ -166,22 +168,27 @@ def sandwich_norm(y: Optional[torch.Tensor], post_w: Optional[torch.Tensor], res
     if nv.use_native(src):
         w_any = post_w if post_w is not None else next_w
         x = torch.empty(rows, cols, dtype=torch.float32, device=src.device)
-        h = torch.empty(rows, cols, dtype=out_dtype, device=src.device) if next_w is not None else None
+        cast_only = next_w is None and cast_next
+        if cast_only and out_dtype == torch.float32:
+            cast_only = False                              # the stream itself is what the next sublayer reads
+        h = torch.empty(rows, cols, dtype=out_dtype, device=src.device) if (next_w is not None or cast_only) else None
         if y is not None:
             y = y.contiguous()
-        fn = nv.proto("b200_sandwich_norm", [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, i32, i32, i32, vp])
+        fn = nv.proto("b200_sandwich_norm", [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, f32, i32, i32, i32, vp])
         nv.check(fn(nv.ptr(y), nv.ptr(post_w), nv.ptr(residual), nv.ptr(x), nv.ptr(next_w), nv.ptr(h), rows, cols, eps,
-                    weight_offset, nv.dtype_code(y.dtype if y is not None else torch.float32), nv.dtype_code(out_dtype),
+                    weight_offset, branch_mult, nv.dtype_code(y.dtype if y is not None else torch.float32), nv.dtype_code(out_dtype),
                     nv.dtype_code(w_any.dtype if w_any is not None else torch.float32), nv.stream()), "sandwich_norm")
         nv.count_launch()
-        return h, x
+        return (x if (h is None and cast_next and next_w is None) else h), x
     x = torch.zeros(rows, cols, dtype=torch.float32, device=src.device) if residual is None else residual.float()
     if y is not None:
         yf = y.float()
         if post_w is not None:
             yf = yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * (weight_offset + post_w.float())
-        x = x + yf
+        x = x + (yf * branch_mult if branch_mult != 1.0 else yf)
     h = None
     if next_w is not None:
         h = (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (weight_offset + next_w.float())).to(out_dtype)
+    elif cast_next:
+        h = x.to(out_dtype)
     return h, x

@@ -22,6 +22,7 @@ import sys
 # kernel sources (csrc/<stem>.cu) behind each served design: what a fresh checkout has to compile before the first step
 NATIVE_SOURCES = {
     "Gorozen": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "paged_attn", "moe"],
+    "Segorax": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "latent_attn", "moe"],
 }
 BLOCK = 64
 MAX_LIVE = 4
