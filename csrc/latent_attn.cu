@@ -14,7 +14,7 @@
 //                          (token, head), a lane per key for the scores and per column for the values.
 //   b200_latent_attn_mma   bf16 on the tensor cores (mma.sync m16n8k16): the 64 rows of a CTA are (token, head) pairs of
 //                          one run of consecutive tokens, all against the same key tile, so both prompt pieces (many
-//                          tokens) and decode tokens (many heads) fill the M dimension. Dk % 16 == 0, Dv <= 256.
+//                          tokens) and decode tokens (many heads) fill the M dimension. Dk % 16 == 0, Dv <= 512.
 //                          `nsplit` > 1 cuts the keys of single-token tiles into ranges that are merged by a second kernel.
 //
 // Causal; an optional per-head sink logit enters the softmax denominator only (running maximum starts at the sink, the
@@ -190,8 +190,10 @@ constexpr int kLQ = 64, kLK = 64;
 // tiles: [n_tiles, 4] = (first row in the batch, rows <= 64, position of the first row, cache row), or NULL: tile t is the
 // single token t at (pos[t], slot[t]). Grid (n_tiles * sub, head blocks, nsplit); sub = sub-tiles of 64 >> hb_log2 tokens.
 // Row r of a CTA is token (r >> hb_log2) of its sub-tile and head h0 + (r & (HB - 1)).
-template <int DVT>                                    // 16 * DVT >= Dv value columns are accumulated
-__global__ void __launch_bounds__(128)
+// With NCOL = 2 the CTA has eight warps: warp w and warp w + 4 own the same 16 rows (both form the scores) and one half of
+// the value columns each, which keeps the accumulators of rows of up to 512 values in registers.
+template <int DVT, int NCOL>                          // 16 * DVT * NCOL >= Dv value columns are accumulated
+__global__ void __launch_bounds__(128 * NCOL)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int* __restrict__ tiles,
                        const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ table, int max_blocks,
                        const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, float* __restrict__ part, int H, int Dk,
@@ -224,25 +226,28 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     k_hi = min(k_hi, k_lo + chunk);
   }
   const int nkb = k_hi > k_lo ? (k_hi - k_lo + kLK - 1) / kLK : 0;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = (tid >> 5) & 3;                     // row group of the warp
+  const int col0 = (tid >> 7) * (16 * DVT);            // first value column of the warp
   const int CH = Dk >> 3, CHL = (LD - 8) >> 3;         // 16-byte chunks of a cache row / of a shared row without its pad
   const int bs_mask = (1 << bs_log2) - 1;
 
-  // two threads per key row, alternating 16-byte chunks (a pair fills whole 32-byte sectors); one page lookup per row
+  // TPR threads per key row, alternating 16-byte chunks (a pair fills whole 32-byte sectors); one page lookup per row
+  constexpr int TPR = 2 * NCOL;
   auto load_k = [&](int buf, int kb) {
-    const int r = tid >> 1, half = tid & 1;
+    const int r = tid / TPR, half = tid % TPR;
     const int kp = k_lo + kb * kLK + r;
     __nv_bfloat16* dk = sk + (buf * kLK + r) * LD;
     if (kp < k_hi) {
       const long long off = ((((long long)trow[kp >> bs_log2]) << bs_log2) + (kp & bs_mask)) * Dk;
-      for (int c = half; c < CH; c += 2) cp_async16(smem_u32(dk + c * 8), cache + off + c * 8);
-      for (int c = CH + half; c < CHL; c += 2) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int c = half; c < CH; c += TPR) cp_async16(smem_u32(dk + c * 8), cache + off + c * 8);
+      for (int c = CH + (half + TPR - CH % TPR) % TPR; c < CHL; c += TPR) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
     } else {
-      for (int c = half; c < CHL; c += 2) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int c = half; c < CHL; c += TPR) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
     }
   };
 
-  for (int c = tid; c < kLQ * CH; c += 128) {
+  for (int c = tid; c < kLQ * CH; c += 128 * NCOL) {
     const int r = c / CH, col = (c % CH) * 8;
     const int tq = r >> hb_log2, h = h0 + (r & (HB - 1));
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -350,7 +355,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
         for (int n = 0; n < 2 * DVT; n += 2) {            // one ldmatrix.x4.trans feeds two output column tiles
           uint32_t b0, b1, b2, b3;
-          ldsm_x4_trans(smem_u32(bk + (kk * 16 + (lane & 15)) * LD + n * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
+          ldsm_x4_trans(smem_u32(bk + (kk * 16 + (lane & 15)) * LD + col0 + n * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
           mma_bf16_16816(o[n], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
           mma_bf16_16816(o[n + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
         }
@@ -367,7 +372,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
 #pragma unroll
     for (int n = 0; n < 2 * DVT; ++n) {
-      const int d = n * 8 + 2 * (lane & 3);
+      const int d = col0 + n * 8 + 2 * (lane & 3);
       if (d >= Dv) continue;
       if (va)
         *reinterpret_cast<uint32_t*>(out + ((long long)(row0 + tok0 + ta) * H + ha) * Dv + d) = pack_bf16x2(o[n][0] * i0, o[n][1] * i0);
@@ -378,13 +383,13 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     // partial (max in the base-2 domain, sum, accumulators) of this key range
     float* pra = part + (((long long)(row0 + tok0 + ta) * H + ha) * nsplit + split) * (Dv + 2);
     float* prb = part + (((long long)(row0 + tok0 + tb) * H + hb) * nsplit + split) * (Dv + 2);
-    if ((lane & 3) == 0) {
+    if ((lane & 3) == 0 && col0 == 0) {
       if (va) { pra[0] = m0; pra[1] = l0; }
       if (vb) { prb[0] = m1; prb[1] = l1; }
     }
 #pragma unroll
     for (int n = 0; n < 2 * DVT; ++n) {
-      const int d = n * 8 + 2 * (lane & 3);
+      const int d = col0 + n * 8 + 2 * (lane & 3);
       if (d >= Dv) continue;
       if (va) { pra[2 + d] = o[n][0]; pra[3 + d] = o[n][1]; }
       if (vb) { prb[2 + d] = o[n][2]; prb[3 + d] = o[n][3]; }
@@ -417,14 +422,14 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part, const f
   }
 }
 
-template <int DVT>
+template <int DVT, int NCOL>
 static int launch_latent_mma(const void* q, const void* cache, const int* tiles, int n_tiles, const int* pos, const int* slot,
                              const int* table, int max_blocks, const float* sinks, void* out, float* part, int H, int Dk, int Dv,
                              int block_size, float scale, int nsplit, cudaStream_t st) {
-  const int LD = (Dk > 16 * DVT ? Dk : 16 * DVT) + 8;
+  const int LD = (Dk > 16 * DVT * NCOL ? Dk : 16 * DVT * NCOL) + 8;
   const size_t smem = (size_t)(kLQ + 2 * kLK) * LD * sizeof(__nv_bfloat16);
   if (smem > 227 * 1024) return B200_ERR_TOO_LARGE;
-  auto kern = latent_attn_mma_kernel<DVT>;
+  auto kern = latent_attn_mma_kernel<DVT, NCOL>;
   if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int bs_log2 = 0;
   while ((1 << bs_log2) < block_size) ++bs_log2;
@@ -434,7 +439,7 @@ static int launch_latent_mma(const void* q, const void* cache, const int* tiles,
   const int HB = 1 << hb_log2;
   const int sub = tiles ? HB : 1;                      // 64 tokens of a tile / (64 / HB) tokens per CTA
   dim3 grid((unsigned)n_tiles * sub, (H + HB - 1) / HB, nsplit);
-  kern<<<grid, 128, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, tiles, pos, slot, table, max_blocks, sinks,
+  kern<<<grid, 128 * NCOL, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, tiles, pos, slot, table, max_blocks, sinks,
                                 (__nv_bfloat16*)out, part, H, Dk, Dv, LD, bs_log2, hb_log2, sub, scale, nsplit);
   B200_LAUNCH_CHECK();
   return 0;
@@ -504,19 +509,21 @@ B200_API int b200_latent_attn_mma(const void* q, const void* cache, const int* t
                                   int Dv, int block_size, float scale, int nsplit, int dtype, void* stream_) {
   cudaStream_t st = (cudaStream_t)stream_;
   if (n_tiles <= 0) return 0;
-  if (dtype != B200_DT_BF16 || Dk % 16 || Dk < 16 || (Dv & 1) || Dv <= 0 || Dv > 256 || Dv > Dk || !(scale > 0.f)) return B200_ERR_UNSUPPORTED;
+  if (dtype != B200_DT_BF16 || Dk % 16 || Dk < 16 || (Dv & 1) || Dv <= 0 || Dv > 512 || Dv > Dk || !(scale > 0.f)) return B200_ERR_UNSUPPORTED;
   if (H <= 0 || block_size <= 0 || nsplit < 1 || (nsplit > 1 && (!part || tiles)) || (!tiles && (!pos || !slot))) return B200_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) return B200_ERR_BAD_ALIGN;
   const int dvt = (Dv + 15) / 16;
-#define LM(N) rc = launch_latent_mma<N>(q, cache, tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, Dk, Dv,      \
-                                        block_size, scale, nsplit, st)
+#define LM(N, NC) rc = launch_latent_mma<N, NC>(q, cache, tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, Dk, Dv,      \
+                                            block_size, scale, nsplit, st)
   int rc;
-  if (dvt <= 2) LM(2);
-  else if (dvt <= 4) LM(4);
-  else if (dvt <= 6) LM(6);
-  else if (dvt <= 8) LM(8);
-  else if (dvt <= 12) LM(12);
-  else LM(16);
+  if (dvt <= 2) LM(2, 1);
+  else if (dvt <= 4) LM(4, 1);
+  else if (dvt <= 6) LM(6, 1);
+  else if (dvt <= 8) LM(8, 1);
+  else if (dvt <= 12) LM(12, 1);
+  else if (dvt <= 16) LM(16, 1);
+  else if (dvt <= 24) LM(12, 2);
+  else LM(16, 2);
 #undef LM
   if (rc) return rc;
   if (nsplit > 1) {

@@ -516,7 +516,7 @@ int b200_latent_q_rope(const void* q, long long q_stride, const float* cos_t, co
 int b200_latent_attn(const void* q, const void* cache, const int* pos, const int* slot, const int* table, int max_blocks,
                      const float* sinks, void* out, int tokens, int H, int Dk, int Dv, int block_size, float scale, int dtype,
                      void* stream);
-/* The same on mma.sync (bf16; Dk % 16 == 0, Dv even and <= 256, block_size a power of two, scale > 0; else
+/* The same on mma.sync (bf16; Dk % 16 == 0, Dv even and <= 512, block_size a power of two, scale > 0; else
  * B200_ERR_UNSUPPORTED). tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row, cache row), or NULL:
  * n_tiles single tokens at (pos, slot), whose keys may be cut into nsplit ranges (part: fp32 [tokens, H, nsplit, Dv + 2]). */
 int b200_latent_attn_mma(const void* q, const void* cache, const int* tiles, int n_tiles, const int* pos, const int* slot,

@@ -10,7 +10,7 @@ of ``q'`` over the cached rows with the rows' first C columns as values (``laten
 no value pool, the block table and the (position, cache row) arrays are those of ``ops.paged_attention``.
 
 Options other designs can use: a query latent with its own norm (or none), rotation of only the first ``rot`` of the R
-columns, per-head attention sinks, any sizes (the tensor-core kernel takes C + R a multiple of 16 and C <= 256; everything
+columns, per-head attention sinks, any sizes (the tensor-core kernel takes C + R a multiple of 16 and C <= 512; everything
 else runs on the fp32-arithmetic kernel).
 """
 from __future__ import annotations
@@ -110,7 +110,7 @@ def latent_attention(qx: torch.Tensor, cache: torch.Tensor, table: torch.Tensor,
         if not qx.is_contiguous() or cache.dtype != qx.dtype:
             raise ValueError("latent_attention: contiguous queries in the cache's dtype")
         out = torch.empty(T, H, Dv, dtype=qx.dtype, device=qx.device)
-        mma_ok = (qx.dtype == torch.bfloat16 and Dk % 16 == 0 and Dv % 2 == 0 and Dv <= 256 and scale > 0 and BS & (BS - 1) == 0
+        mma_ok = (qx.dtype == torch.bfloat16 and Dk % 16 == 0 and Dv % 2 == 0 and Dv <= 512 and scale > 0 and BS & (BS - 1) == 0
                   and (Dk + 8) * 2 * 192 <= 227 * 1024 and os.environ.get("B200_LATENT_MMA", "1") != "0")
         if mma_ok:
             fn = nv.proto("b200_latent_attn_mma", [vp, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, vp])
