@@ -271,7 +271,8 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
   for (int i = 0; i < 2 * DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const int qpa = qp0 + ta, qpb = qp0 + tb;            // positions of this thread's two rows
-  const bool warp_live = ((warp * 16) >> hb_log2) < ntok;      // a warp none of whose rows is a token only helps loading
+  // a warp none of whose rows is a token of the piece and a head of the model only helps loading
+  const bool warp_live = ((warp * 16) >> hb_log2) < ntok && (HB < 16 || h0 + ((warp * 16) & (HB - 1)) < H);
   const int dkt = Dk >> 4;
 
   for (int kb = 0; kb < nkb; ++kb) {
@@ -434,8 +435,18 @@ static int launch_latent_mma(const void* q, const void* cache, const int* tiles,
   int bs_log2 = 0;
   while ((1 << bs_log2) < block_size) ++bs_log2;
   if ((1 << bs_log2) != block_size) return B200_ERR_UNSUPPORTED;
+  // heads per CTA (a power of two): single tokens want all heads in one CTA, so that the keys are read once; pieces have
+  // tokens to fill the rows with and take the split that leaves the fewest rows to padding heads (ties: more heads)
   int hb_log2 = 0;
   while ((1 << hb_log2) < H && hb_log2 < 6) ++hb_log2;
+  if (tiles) {
+    int best = hb_log2, waste = ((H + (1 << hb_log2) - 1) >> hb_log2 << hb_log2) - H;
+    for (int c = hb_log2 - 1; c >= 0 && waste > 0; --c) {
+      const int w = ((H + (1 << c) - 1) >> c << c) - H;
+      if (w < waste) { best = c; waste = w; }
+    }
+    hb_log2 = best;
+  }
   const int HB = 1 << hb_log2;
   const int sub = tiles ? HB : 1;                      // 64 tokens of a tile / (64 / HB) tokens per CTA
   dim3 grid((unsigned)n_tiles * sub, (H + HB - 1) / HB, nsplit);
