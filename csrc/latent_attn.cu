@@ -7,7 +7,7 @@
 // gathered in the latent space too, sum_j p_j c_j [C], and expanded by W_uv_h afterwards. For the attention kernel this
 // is multi-query attention whose keys have Dk dims and whose values are the first Dv = C dims of the same rows.
 //
-//   b200_latent_kv_store   one CTA per token: RMS norm of the query latent (optional) and of c, rotary embedding of r
+//   b200_latent_kv_store   one warp per token: RMS norm of the query latent (optional) and of c, rotary embedding of r
 //                          (interleaved pairs, tables indexed by position), [c | r] -> the token's row of its cache page.
 //   b200_latent_q_rope     rotated part of every query head -> columns C .. C + R of the attention's query rows.
 //   b200_latent_attn       fp32 arithmetic over a 16-bit or 32-bit cache, any sizes (Dk <= 1024, Dv <= 512): a warp per
@@ -30,63 +30,78 @@ namespace b200 {
 // ------------------------------------------------------------------------------------------------------------------
 // proj: fp32 [tokens, ld]: columns [q_off, q_off + Cq) the query latent (Cq may be 0), [kv_off, kv_off + C) the KV latent,
 // then R columns of the shared rotated key part. cq_out [tokens, Cq]; cache rows of Dk = C + R.
+// One warp per token (the latents are a few hundred values: warp reductions only, no block barrier).
 template <typename T, typename WT>
 __global__ void __launch_bounds__(128)
 latent_kv_store_kernel(const float* __restrict__ proj, long long ld, int q_off, int Cq, int kv_off, int C, int R, int rot,
                        const WT* __restrict__ wq, const WT* __restrict__ wkv, float eps, const float* __restrict__ cs,
                        const float* __restrict__ sn, const int* __restrict__ pos, const int* __restrict__ slot,
                        const int* __restrict__ table, int max_blocks, int block_size, T* __restrict__ cq_out,
-                       T* __restrict__ cache) {
-  __shared__ float red[32];
-  const long long t = blockIdx.x;
+                       T* __restrict__ cache, int tokens) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
   const float* row = proj + t * ld;
   const int p = pos[t];
-  if (Cq > 0) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < Cq; i += blockDim.x) { const float v = row[q_off + i]; ss += v * v; }
-    ss = block_sum(ss, red);
-    const float r = 1.f / sqrtf(ss / (float)Cq + eps);
-    for (int i = threadIdx.x; i < Cq; i += blockDim.x) cq_out[t * Cq + i] = from_f32<T>(row[q_off + i] * r * to_f32<WT>(wq[i]));
-  }
   const int blk = table[(long long)slot[t] * max_blocks + p / block_size];
   T* dst = cache + ((long long)blk * block_size + p % block_size) * (C + R);
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = row[kv_off + i]; ss += v * v; }
-  ss = block_sum(ss, red);
-  const float r = 1.f / sqrtf(ss / (float)C + eps);
-  for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = from_f32<T>(row[kv_off + i] * r * to_f32<WT>(wkv[i]));
+  // the rotated key part first: its loads do not wait for a reduction
   const float* kr = row + kv_off + C;
   const int hr = rot / 2;
-  for (int i = threadIdx.x; i < hr; i += blockDim.x) {
+  for (int i = lane; i < hr; i += 32) {
     const float u = kr[2 * i], v = kr[2 * i + 1];
     const float c = cs[(long long)p * hr + i], s = sn[(long long)p * hr + i];
     dst[C + 2 * i] = from_f32<T>(u * c - v * s);
     dst[C + 2 * i + 1] = from_f32<T>(v * c + u * s);
   }
-  for (int i = rot + threadIdx.x; i < R; i += blockDim.x) dst[C + i] = from_f32<T>(kr[i]);
+  for (int i = rot + lane; i < R; i += 32) dst[C + i] = from_f32<T>(kr[i]);
+  float ss = 0.f, sq = 0.f;
+  for (int i = lane; i < C; i += 32) { const float v = row[kv_off + i]; ss += v * v; }
+  for (int i = lane; i < Cq; i += 32) { const float v = row[q_off + i]; sq += v * v; }
+  ss = warp_sum(ss);
+  sq = warp_sum(sq);
+  const float r = 1.f / sqrtf(ss / (float)C + eps);
+  for (int i = lane; i < C; i += 32) dst[i] = from_f32<T>(row[kv_off + i] * r * to_f32<WT>(wkv[i]));
+  if (Cq > 0) {
+    const float rq = 1.f / sqrtf(sq / (float)Cq + eps);
+    for (int i = lane; i < Cq; i += 32) cq_out[t * Cq + i] = from_f32<T>(row[q_off + i] * rq * to_f32<WT>(wq[i]));
+  }
 }
 
-// q [tokens, q_stride]: head h at h * (D + R), its last R columns are the rotated part -> qx[t, h, C + i]
+// q [tokens, q_stride]: head h at h * (D + R), its last R columns are the rotated part -> qx[t, h, C + i]. A thread turns
+// one pair; `pair2` says that pairs may be moved as one 32-bit word (16-bit type, even offsets).
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_q_rope_kernel(const T* __restrict__ q, long long q_stride, const float* __restrict__ cs, const float* __restrict__ sn,
-                     const int* __restrict__ pos, T* __restrict__ qx, int H, int D, int R, int rot, int C) {
-  const long long t = blockIdx.x;
-  const int p = pos[t];
+                     const int* __restrict__ pos, T* __restrict__ qx, int tokens, int H, int D, int R, int rot, int C, int pair2) {
   const int hr = rot / 2;
   const int items = hr + (R - rot);
-  for (int w = threadIdx.x; w < H * items; w += blockDim.x) {
-    const int h = w / items, i = w % items;
-    const T* src = q + t * q_stride + (long long)h * (D + R) + D;
-    T* dst = qx + (t * H + h) * (long long)(C + R) + C;
-    if (i < hr) {
-      const float u = to_f32<T>(src[2 * i]), v = to_f32<T>(src[2 * i + 1]);
-      const float c = cs[(long long)p * hr + i], s = sn[(long long)p * hr + i];
+  const long long per_tok = (long long)H * items;
+  const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= per_tok * tokens) return;
+  const long long t = w / per_tok;
+  const int rem = (int)(w - t * per_tok);
+  const int h = rem / items, i = rem % items;
+  const int p = pos[t];
+  const T* src = q + t * q_stride + (long long)h * (D + R) + D;
+  T* dst = qx + (t * H + h) * (long long)(C + R) + C;
+  if (i < hr) {
+    float u, v;
+    if (sizeof(T) == 2 && pair2) {
+      const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(src + 2 * i));
+      u = f.x; v = f.y;
+    } else {
+      u = to_f32<T>(src[2 * i]); v = to_f32<T>(src[2 * i + 1]);
+    }
+    const float c = cs[(long long)p * hr + i], s = sn[(long long)p * hr + i];
+    if (sizeof(T) == 2 && pair2) {
+      *reinterpret_cast<uint32_t*>(dst + 2 * i) = pack_bf16x2(u * c - v * s, v * c + u * s);
+    } else {
       dst[2 * i] = from_f32<T>(u * c - v * s);
       dst[2 * i + 1] = from_f32<T>(v * c + u * s);
-    } else {
-      dst[rot + i - hr] = src[rot + i - hr];
     }
+  } else {
+    dst[rot + i - hr] = src[rot + i - hr];
   }
 }
 
@@ -192,7 +207,9 @@ constexpr int kLQ = 64, kLK = 64;
 // Row r of a CTA is token (r >> hb_log2) of its sub-tile and head h0 + (r & (HB - 1)).
 // With NCOL = 2 the CTA has eight warps: warp w and warp w + 4 own the same 16 rows (both form the scores) and one half of
 // the value columns each, which keeps the accumulators of rows of up to 512 values in registers.
-template <int DVT, int NCOL>                          // 16 * DVT * NCOL >= Dv value columns are accumulated
+// With KS (single tokens of at most 16 heads: one row group is all the CTA has) the four row-group warps all take rows 0 .. 15
+// and a quarter of every key tile each, and their (max, sum, accumulator) triples are merged through shared memory at the end.
+template <int DVT, int NCOL, bool KS>                 // 16 * DVT * NCOL >= Dv value columns are accumulated
 __global__ void __launch_bounds__(128 * NCOL)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int* __restrict__ tiles,
                        const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ table, int max_blocks,
@@ -227,7 +244,11 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   }
   const int nkb = k_hi > k_lo ? (k_hi - k_lo + kLK - 1) / kLK : 0;
   const int tid = threadIdx.x, lane = tid & 31;
-  const int warp = (tid >> 5) & 3;                     // row group of the warp
+  const int wq = (tid >> 5) & 3;
+  const int warp = KS ? 0 : wq;                        // row group of the warp
+  constexpr int NT = KS ? 2 : 8;                       // key tiles of 8 a warp scores per 64-key block, starting at tile n0
+  constexpr int KK = KS ? 1 : 4;                       // k-steps of 16 keys in its P V product, starting at step kk0
+  const int n0 = KS ? 2 * wq : 0, kk0 = KS ? wq : 0;
   const int col0 = (tid >> 7) * (16 * DVT);            // first value column of the warp
   const int CH = Dk >> 3, CHL = (LD - 8) >> 3;         // 16-byte chunks of a cache row / of a shared row without its pad
   const int bs_mask = (1 << bs_log2) - 1;
@@ -283,39 +304,39 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     __syncthreads();
     if (warp_live) {
       const __nv_bfloat16* bk = sk + buf * kLK * LD;
-      float s[8][4];
+      float s[NT][4];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
       const __nv_bfloat16* qrow = sq + (warp * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
-      const __nv_bfloat16* krow = bk + (lane & 7) * LD + (lane >> 3) * 8;
+      const __nv_bfloat16* krow = bk + (n0 * 8 + (lane & 7)) * LD + (lane >> 3) * 8;
       int k = 0;
 #pragma unroll 1
       for (; k + 1 < dkt; k += 2) {                      // one ldmatrix.x4 of K feeds two k-steps of a key tile
-        uint32_t a[2][4], b[8][4];
+        uint32_t a[2][4], b[NT][4];
         ldsm_x4(smem_u32(qrow + k * 16), a[0][0], a[0][1], a[0][2], a[0][3]);
         ldsm_x4(smem_u32(qrow + k * 16 + 16), a[1][0], a[1][1], a[1][2], a[1][3]);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) ldsm_x4(smem_u32(krow + n * 8 * LD + k * 16), b[n][0], b[n][1], b[n][2], b[n][3]);
+        for (int n = 0; n < NT; ++n) ldsm_x4(smem_u32(krow + n * 8 * LD + k * 16), b[n][0], b[n][1], b[n][2], b[n][3]);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], a[0][0], a[0][1], a[0][2], a[0][3], b[n][0], b[n][1]);
+        for (int n = 0; n < NT; ++n) mma_bf16_16816(s[n], a[0][0], a[0][1], a[0][2], a[0][3], b[n][0], b[n][1]);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], a[1][0], a[1][1], a[1][2], a[1][3], b[n][2], b[n][3]);
+        for (int n = 0; n < NT; ++n) mma_bf16_16816(s[n], a[1][0], a[1][1], a[1][2], a[1][3], b[n][2], b[n][3]);
       }
       if (k < dkt) {
-        uint32_t a[4], b[8][2];
+        uint32_t a[4], b[NT][2];
         ldsm_x4(smem_u32(qrow + k * 16), a[0], a[1], a[2], a[3]);
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
-          ldsm_x2(smem_u32(bk + (n * 8 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8), b[n][0], b[n][1]);
+        for (int n = 0; n < NT; ++n)
+          ldsm_x2(smem_u32(bk + ((n0 + n) * 8 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8), b[n][0], b[n][1]);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) mma_bf16_16816(s[n], a[0], a[1], a[2], a[3], b[n][0], b[n][1]);
+        for (int n = 0; n < NT; ++n) mma_bf16_16816(s[n], a[0], a[1], a[2], a[3], b[n][0], b[n][1]);
       }
       // causal mask and the end of the key range, only in blocks that reach past the warp's first position or the range
       const int kbase0 = k_lo + kb * kLK;
       if (kbase0 + kLK - 1 > qp0 + ((warp * 16) >> hb_log2) || kbase0 + kLK > k_hi) {
-        const int kbase = kbase0 + 2 * (lane & 3);
+        const int kbase = kbase0 + n0 * 8 + 2 * (lane & 3);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < NT; ++n) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int key = kbase + n * 8 + (j & 1);
@@ -325,7 +346,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       }
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < NT; ++n) {
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
       }
@@ -340,9 +361,9 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       l0 *= r0; l1 *= r1;
 #pragma unroll
       for (int i = 0; i < 2 * DVT; ++i) { o[i][0] *= r0; o[i][1] *= r0; o[i][2] *= r1; o[i][3] *= r1; }
-      uint32_t pa[4][4];                                  // P as A fragments: 4 k-steps of 16 keys
+      uint32_t pa[KK][4];                                 // P as A fragments: k-steps of 16 keys
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < NT; ++n) {
         const float p0 = ex2_approx(fmaf(s[n][0], sl2, -e0)), p1 = ex2_approx(fmaf(s[n][1], sl2, -e0));
         const float p2 = ex2_approx(fmaf(s[n][2], sl2, -e1)), p3 = ex2_approx(fmaf(s[n][3], sl2, -e1));
         l0 += p0 + p1;
@@ -352,11 +373,11 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       }
       // the values are the first columns of the key rows
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
+      for (int kk = 0; kk < KK; ++kk) {
 #pragma unroll
         for (int n = 0; n < 2 * DVT; n += 2) {            // one ldmatrix.x4.trans feeds two output column tiles
           uint32_t b0, b1, b2, b3;
-          ldsm_x4_trans(smem_u32(bk + (kk * 16 + (lane & 15)) * LD + col0 + n * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
+          ldsm_x4_trans(smem_u32(bk + ((kk0 + kk) * 16 + (lane & 15)) * LD + col0 + n * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
           mma_bf16_16816(o[n], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
           mma_bf16_16816(o[n + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
         }
@@ -368,6 +389,55 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (KS) {
+    // the four key quarters of rows 0 .. 15 meet in shared memory (the key buffers are free: the loop ended on a barrier)
+    float* mg = reinterpret_cast<float*>(sk);            // [4][16][Dv + 2]
+    const int W2 = Dv + 2;
+    float* wa = mg + (wq * 16 + ra) * W2;
+    float* wb = mg + (wq * 16 + rb) * W2;
+    if ((lane & 3) == 0 && col0 == 0) {
+      // the running maximum is only the reference point of the sum and the accumulators (it may be the sink's start value);
+      // the sink's own term enters once, below
+      wa[0] = m0; wa[1] = l0;
+      wb[0] = m1; wb[1] = l1;
+    }
+#pragma unroll
+    for (int n = 0; n < 2 * DVT; ++n) {
+      const int d = col0 + n * 8 + 2 * (lane & 3);
+      if (d >= Dv) continue;
+      wa[2 + d] = o[n][0]; wa[3 + d] = o[n][1];
+      wb[2 + d] = o[n][2]; wb[3 + d] = o[n][3];
+    }
+    __syncthreads();
+    for (int i = tid; i < 16 * Dv; i += 128 * NCOL) {
+      const int r = i / Dv, d = i - r * Dv;
+      const int h = h0 + (r & (HB - 1));
+      if ((r >> hb_log2) >= ntok || h >= H) continue;
+      const float sk2 = own_sink ? sinks[h] * LOG2E : -INFINITY;
+      float m = sk2;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, mg[(w * 16 + r) * W2]);
+      float l = own_sink ? exp2f(sk2 - m) : 0.f, a = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float* ws = mg + (w * 16 + r) * W2;
+        if (ws[0] != -INFINITY) {
+          const float e = exp2f(ws[0] - m);
+          l += ws[1] * e;
+          a += ws[2 + d] * e;
+        }
+      }
+      const long long orow = (long long)(row0 + tok0 + (r >> hb_log2)) * H + h;
+      if (nsplit == 1) {
+        out[orow * Dv + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+      } else {
+        float* pr = part + (orow * nsplit + split) * W2;
+        if (d == 0) { pr[0] = m; pr[1] = l; }
+        pr[2 + d] = a;
+      }
+    }
+    return;
+  }
   if (nsplit == 1) {
     if (own_sink) { l0 += ex2_approx(sinka - m0); l1 += ex2_approx(sinkb - m1); }
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
@@ -423,14 +493,14 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part, const f
   }
 }
 
-template <int DVT, int NCOL>
+template <int DVT, int NCOL, bool KS>
 static int launch_latent_mma(const void* q, const void* cache, const int* tiles, int n_tiles, const int* pos, const int* slot,
                              const int* table, int max_blocks, const float* sinks, void* out, float* part, int H, int Dk, int Dv,
                              int block_size, float scale, int nsplit, cudaStream_t st) {
   const int LD = (Dk > 16 * DVT * NCOL ? Dk : 16 * DVT * NCOL) + 8;
   const size_t smem = (size_t)(kLQ + 2 * kLK) * LD * sizeof(__nv_bfloat16);
   if (smem > 227 * 1024) return B200_ERR_TOO_LARGE;
-  auto kern = latent_attn_mma_kernel<DVT, NCOL>;
+  auto kern = latent_attn_mma_kernel<DVT, NCOL, KS>;
   if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int bs_log2 = 0;
   while ((1 << bs_log2) < block_size) ++bs_log2;
@@ -469,8 +539,9 @@ B200_API int b200_latent_kv_store(const float* proj, long long ld, int q_off, in
   if (C <= 0 || R < 0 || rot < 0 || rot > R || (rot & 1) || Cq < 0 || block_size <= 0) return B200_ERR_BAD_SHAPE;
   typedef __nv_bfloat16 bf;
 #define KS(T, WT)                                                                                                             \
-  latent_kv_store_kernel<T, WT><<<tokens, 128, 0, st>>>(proj, ld, q_off, Cq, kv_off, C, R, rot, (const WT*)wq, (const WT*)wkv, eps, \
-                                                        cos_t, sin_t, pos, slot, table, max_blocks, block_size, (T*)cq_out, (T*)cache)
+  latent_kv_store_kernel<T, WT><<<(tokens + 3) / 4, 128, 0, st>>>(proj, ld, q_off, Cq, kv_off, C, R, rot, (const WT*)wq,            \
+                                                                  (const WT*)wkv, eps, cos_t, sin_t, pos, slot, table, max_blocks, \
+                                                                  block_size, (T*)cq_out, (T*)cache, tokens)
   if (dtype == B200_DT_BF16 && w_dtype == B200_DT_BF16) KS(bf, bf);
   else if (dtype == B200_DT_BF16 && w_dtype == B200_DT_FP32) KS(bf, float);
   else if (dtype == B200_DT_FP32 && w_dtype == B200_DT_FP32) KS(float, float);
@@ -486,10 +557,15 @@ B200_API int b200_latent_q_rope(const void* q, long long q_stride, const float* 
   cudaStream_t st = (cudaStream_t)stream_;
   if (tokens <= 0 || R == 0) return 0;
   if (H <= 0 || D < 0 || R < 0 || rot < 0 || rot > R || (rot & 1) || C <= 0) return B200_ERR_BAD_SHAPE;
+  const long long work = (long long)tokens * H * (rot / 2 + R - rot);
+  const unsigned grid = (unsigned)((work + 255) / 256);
+  // a pair is one aligned 32-bit word when every offset that leads to it is even
+  const int pair2 = !((q_stride | D | R | C) & 1) && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(qx)) & 3);
   if (dtype == B200_DT_BF16)
-    latent_q_rope_kernel<__nv_bfloat16><<<tokens, 128, 0, st>>>((const __nv_bfloat16*)q, q_stride, cos_t, sin_t, pos, (__nv_bfloat16*)qx, H, D, R, rot, C);
+    latent_q_rope_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, q_stride, cos_t, sin_t, pos, (__nv_bfloat16*)qx,
+                                                              tokens, H, D, R, rot, C, pair2);
   else if (dtype == B200_DT_FP32)
-    latent_q_rope_kernel<float><<<tokens, 128, 0, st>>>((const float*)q, q_stride, cos_t, sin_t, pos, (float*)qx, H, D, R, rot, C);
+    latent_q_rope_kernel<float><<<grid, 256, 0, st>>>((const float*)q, q_stride, cos_t, sin_t, pos, (float*)qx, tokens, H, D, R, rot, C, 0);
   else return B200_ERR_UNSUPPORTED;
   B200_LAUNCH_CHECK();
   return 0;
@@ -524,7 +600,12 @@ B200_API int b200_latent_attn_mma(const void* q, const void* cache, const int* t
   if (H <= 0 || block_size <= 0 || nsplit < 1 || (nsplit > 1 && (!part || tiles)) || (!tiles && (!pos || !slot))) return B200_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) return B200_ERR_BAD_ALIGN;
   const int dvt = (Dv + 15) / 16;
-#define LM(N, NC) rc = launch_latent_mma<N, NC>(q, cache, tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, Dk, Dv,      \
+  // single tokens of at most 16 heads occupy one row group: its four warps split the keys of a tile instead
+  const bool ks = !tiles && H <= 16;
+#define LM(N, NC)                                                                                                              \
+  rc = ks ? launch_latent_mma<N, NC, true>(q, cache, (const int*)nullptr, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, \
+                                           Dk, Dv, block_size, scale, nsplit, st)                                                  \
+          : launch_latent_mma<N, NC, false>(q, cache, tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, Dk, Dv,      \
                                             block_size, scale, nsplit, st)
   int rc;
   if (dvt <= 2) LM(2, 1);

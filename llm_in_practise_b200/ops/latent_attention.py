@@ -92,7 +92,7 @@ def latent_q_rope(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: to
     return qx
 
 
-_SPLIT_KEYS = int(os.environ.get("B200_LATENT_SPLIT_KEYS", "512"))      # keys per split of a decode-only batch
+_SPLIT_KEYS = int(os.environ.get("B200_LATENT_SPLIT_KEYS", "256"))      # keys per split of a decode-only batch
 
 
 def latent_attention(qx: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor,

@@ -229,7 +229,8 @@ def _latent_reference(q, rows, C, scale, sink):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("H,C,R,BS", [(4, 40, 8, 64), (3, 36, 6, 16), (6, 64, 32, 64), (1, 16, 16, 32), (16, 32, 16, 64), (80, 16, 0, 64)])
+@pytest.mark.parametrize("H,C,R,BS", [(4, 40, 8, 64), (3, 36, 6, 16), (6, 64, 32, 64), (1, 16, 16, 32), (16, 32, 16, 64), (80, 16, 0, 64),
+                                      (2, 320, 16, 64), (20, 272, 16, 64), (40, 128, 32, 64)])
 @pytest.mark.parametrize("with_sink", [True, False])
 def test_latent_attention(device, dtype, H, C, R, BS, with_sink):
     from llm_in_practise_b200.ops.latent_attention import latent_attention
