@@ -209,15 +209,17 @@ constexpr int kLQ = 64, kLK = 64;
 // the value columns each, which keeps the accumulators of rows of up to 512 values in registers.
 // With KS (single tokens of at most 16 heads: one row group is all the CTA has) the four row-group warps all take rows 0 .. 15
 // and a quarter of every key tile each, and their (max, sum, accumulator) triples are merged through shared memory at the end.
-template <int DVT, int NCOL, bool KS>                 // 16 * DVT * NCOL >= Dv value columns are accumulated
+// NS key tiles are in flight or in use at a time (a decode CTA does little math per tile: what it needs is bytes in flight).
+template <int DVT, int NCOL, bool KS, int NS>         // 16 * DVT * NCOL >= Dv value columns are accumulated
 __global__ void __launch_bounds__(128 * NCOL)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int* __restrict__ tiles,
                        const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ table, int max_blocks,
                        const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, float* __restrict__ part, int H, int Dk,
                        int Dv, int LD, int bs_log2, int hb_log2, int sub, float scale, int nsplit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][LD]
-  __nv_bfloat16* sk = sq + kLQ * LD;                                          // [2][64][LD]
+  constexpr int QR = KS ? 16 : kLQ;                    // query rows held
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [QR][LD]
+  __nv_bfloat16* sk = sq + QR * LD;                                           // [NS][64][LD]
   const int HB = 1 << hb_log2;
   const int tq_cta = kLQ >> hb_log2;                   // tokens per CTA
   // later tiles of a piece see more keys: taking them first keeps the long CTAs out of the last wave
@@ -253,30 +255,55 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int CH = Dk >> 3, CHL = (LD - 8) >> 3;         // 16-byte chunks of a cache row / of a shared row without its pad
   const int bs_mask = (1 << bs_log2) - 1;
 
-  // TPR threads per key row, alternating 16-byte chunks (a pair fills whole 32-byte sectors); one page lookup per row
-  constexpr int TPR = 2 * NCOL;
+  // consecutive threads fetch consecutive 16-byte chunks of the tile; rows past the key range are zeroed. A thread walks its
+  // chunks (row r, chunk c of the row) by increments: no division per chunk. With pages of 64 rows or more a tile lies
+  // inside one page (key ranges start at multiples of 64), where its rows are back to back: chunk idx of the tile is at
+  // 16 * idx bytes from the first row, so a warp's request covers 512 contiguous bytes and the page is looked up once.
+  constexpr int NTHR = 128 * NCOL;
+  const int ld_r0 = tid / CH, ld_c0 = tid - ld_r0 * CH, ld_dr = NTHR / CH, ld_dc = NTHR - ld_dr * CH;
   auto load_k = [&](int buf, int kb) {
-    const int r = tid / TPR, half = tid % TPR;
-    const int kp = k_lo + kb * kLK + r;
-    __nv_bfloat16* dk = sk + (buf * kLK + r) * LD;
-    if (kp < k_hi) {
-      const long long off = ((((long long)trow[kp >> bs_log2]) << bs_log2) + (kp & bs_mask)) * Dk;
-      for (int c = half; c < CH; c += TPR) cp_async16(smem_u32(dk + c * 8), cache + off + c * 8);
-      for (int c = CH + (half + TPR - CH % TPR) % TPR; c < CHL; c += TPR) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+    const int kp0 = k_lo + kb * kLK;
+    const int nvalid = min(kLK, k_hi - kp0);
+    __nv_bfloat16* dbase = sk + buf * kLK * LD;
+    int r = ld_r0, c = ld_c0;
+    if (bs_log2 >= 6) {
+      const __nv_bfloat16* src = cache + ((((long long)trow[kp0 >> bs_log2]) << bs_log2) + (kp0 & bs_mask)) * Dk;
+      for (int idx = tid; idx < kLK * CH; idx += NTHR) {
+        __nv_bfloat16* dk = dbase + r * LD + c * 8;
+        if (r < nvalid) cp_async16(smem_u32(dk), src + (long long)idx * 8);
+        else *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+        c += ld_dc; r += ld_dr;
+        if (c >= CH) { c -= CH; ++r; }
+      }
     } else {
-      for (int c = half; c < CHL; c += TPR) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int idx = tid; idx < kLK * CH; idx += NTHR) {
+        __nv_bfloat16* dk = dbase + r * LD + c * 8;
+        const int kp = kp0 + r;
+        if (r < nvalid)
+          cp_async16(smem_u32(dk), cache + ((((long long)trow[kp >> bs_log2]) << bs_log2) + (kp & bs_mask)) * Dk + c * 8);
+        else *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+        c += ld_dc; r += ld_dr;
+        if (c >= CH) { c -= CH; ++r; }
+      }
     }
   };
+  // columns between the row's end and the accumulated value columns (narrow rows only) stay zero in every buffer
+  if (CHL > CH)
+    for (int idx = tid; idx < NS * kLK * (CHL - CH); idx += NTHR)
+      *reinterpret_cast<uint4*>(sk + (idx / (CHL - CH)) * LD + (CH + idx % (CHL - CH)) * 8) = make_uint4(0, 0, 0, 0);
 
-  for (int c = tid; c < kLQ * CH; c += 128 * NCOL) {
+  for (int c = tid; c < QR * CH; c += NTHR) {
     const int r = c / CH, col = (c % CH) * 8;
     const int tq = r >> hb_log2, h = h0 + (r & (HB - 1));
     uint4 v = make_uint4(0, 0, 0, 0);
     if (tq < ntok && h < H) v = *reinterpret_cast<const uint4*>(q + ((long long)(row0 + tok0 + tq) * H + h) * Dk + col);
     *reinterpret_cast<uint4*>(sq + r * LD + col) = v;
   }
-  if (nkb > 0) load_k(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int st0 = 0; st0 < NS - 1; ++st0) {               // tiles 0 .. NS - 2, a group each
+    if (st0 < nkb) load_k(st0, st0);
+    cp_async_commit();
+  }
 
   const float LOG2E = 1.4426950408889634f;
   const float sl2 = scale * LOG2E;
@@ -297,10 +324,10 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int dkt = Dk >> 4;
 
   for (int kb = 0; kb < nkb; ++kb) {
-    const int buf = kb & 1;
-    if (kb + 1 < nkb) load_k(buf ^ 1, kb + 1);
+    const int buf = kb % NS;
+    if (kb + NS - 1 < nkb) load_k((kb + NS - 1) % NS, kb + NS - 1);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<NS - 1>();
     __syncthreads();
     if (warp_live) {
       const __nv_bfloat16* bk = sk + buf * kLK * LD;
@@ -493,14 +520,14 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part, const f
   }
 }
 
-template <int DVT, int NCOL, bool KS>
+template <int DVT, int NCOL, bool KS, int NS>
 static int launch_latent_mma(const void* q, const void* cache, const int* tiles, int n_tiles, const int* pos, const int* slot,
                              const int* table, int max_blocks, const float* sinks, void* out, float* part, int H, int Dk, int Dv,
                              int block_size, float scale, int nsplit, cudaStream_t st) {
   const int LD = (Dk > 16 * DVT * NCOL ? Dk : 16 * DVT * NCOL) + 8;
-  const size_t smem = (size_t)(kLQ + 2 * kLK) * LD * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)((KS ? 16 : kLQ) + NS * kLK) * LD * sizeof(__nv_bfloat16);
   if (smem > 227 * 1024) return B200_ERR_TOO_LARGE;
-  auto kern = latent_attn_mma_kernel<DVT, NCOL, KS>;
+  auto kern = latent_attn_mma_kernel<DVT, NCOL, KS, NS>;
   if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int bs_log2 = 0;
   while ((1 << bs_log2) < block_size) ++bs_log2;
@@ -601,12 +628,14 @@ B200_API int b200_latent_attn_mma(const void* q, const void* cache, const int* t
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) return B200_ERR_BAD_ALIGN;
   const int dvt = (Dv + 15) / 16;
   // single tokens of at most 16 heads occupy one row group: its four warps split the keys of a tile instead
-  const bool ks = !tiles && H <= 16;
-#define LM(N, NC)                                                                                                              \
-  rc = ks ? launch_latent_mma<N, NC, true>(q, cache, (const int*)nullptr, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, \
-                                           Dk, Dv, block_size, scale, nsplit, st)                                                  \
-          : launch_latent_mma<N, NC, false>(q, cache, tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, part, H, Dk, Dv,      \
-                                            block_size, scale, nsplit, st)
+  static const bool ks_on = [] { const char* e = getenv("B200_LATENT_KEYSPLIT"); return !(e && e[0] == '0'); }();
+  const bool ks = !tiles && H <= 16 && ks_on;
+  // ... with three key tiles in flight where two such CTAs still fit an SM
+  const int ld_max = (Dk > 16 * ((dvt + 1) / 2 * 2) ? Dk : 16 * ((dvt + 1) / 2 * 2)) + 8;
+  const bool ns3 = ks && (size_t)(16 + 3 * kLK) * ld_max * sizeof(__nv_bfloat16) <= 110 * 1024;
+#define LMA(N, NC, K, S) launch_latent_mma<N, NC, K, S>(q, cache, (const int*)tiles, n_tiles, pos, slot, table, max_blocks, sinks, out, \
+                                                        part, H, Dk, Dv, block_size, scale, nsplit, st)
+#define LM(N, NC) rc = ks ? (ns3 ? LMA(N, NC, true, 3) : LMA(N, NC, true, 2)) : LMA(N, NC, false, 2)
   int rc;
   if (dvt <= 2) LM(2, 1);
   else if (dvt <= 4) LM(4, 1);
@@ -617,6 +646,7 @@ B200_API int b200_latent_attn_mma(const void* q, const void* cache, const int* t
   else if (dvt <= 24) LM(12, 2);
   else LM(16, 2);
 #undef LM
+#undef LMA
   if (rc) return rc;
   if (nsplit > 1) {
     latent_attn_merge_kernel<<<dim3(n_tiles, H), 64, 0, st>>>(part, sinks, (__nv_bfloat16*)out, H, Dv, nsplit);

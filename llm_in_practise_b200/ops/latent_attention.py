@@ -126,7 +126,7 @@ def latent_attention(qx: torch.Tensor, cache: torch.Tensor, table: torch.Tensor,
             ctas = T * -(-H // hb)
             nsplit = 1
             if max_pos > 2 * _SPLIT_KEYS and ctas < 296:
-                nsplit = min(32, -(-max_pos // _SPLIT_KEYS), max(1, 592 // ctas))
+                nsplit = min(32, -(-max_pos // _SPLIT_KEYS), max(1, 296 // ctas))
             part = torch.empty(T * H * nsplit * (Dv + 2), dtype=torch.float32, device=qx.device) if nsplit > 1 else None
             nv.check(fn(nv.ptr(qx), nv.ptr(cache), None, T, nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1], nv.ptr(sinks),
                         nv.ptr(out), nv.ptr(part), H, Dk, Dv, BS, scale, nsplit, nv.dtype_code(qx.dtype), nv.stream()),
