@@ -628,6 +628,7 @@ B200_API int b200_latent_attn_mma(const void* q, const void* cache, const int* t
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) return B200_ERR_BAD_ALIGN;
   const int dvt = (Dv + 15) / 16;
   // single tokens of at most 16 heads occupy one row group: its four warps split the keys of a tile instead
+  // (B200_LATENT_KEYSPLIT=0 switches that off, for measurements)
   static const bool ks_on = [] { const char* e = getenv("B200_LATENT_KEYSPLIT"); return !(e && e[0] == '0'); }();
   const bool ks = !tiles && H <= 16 && ks_on;
   // ... with three key tiles in flight where two such CTAs still fit an SM

@@ -106,7 +106,7 @@ moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, co
       }
       gs[g] = sum;
     }
-    for (int k = 0; k < keep; ++k) {                   // mark the kept groups with NaN-free flags: +inf = kept
+    for (int k = 0; k < keep; ++k) {                   // the `keep` best groups, marked by a score of +inf
       int best = -1;
       float bv = -INFINITY;
       for (int g = 0; g < groups; ++g)
